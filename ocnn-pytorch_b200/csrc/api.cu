@@ -1,0 +1,165 @@
+// C-ABI glue: error reporting, device queries and the convolution entry points
+// (argument validation, workspace carving and kernel selection).
+#include <stdarg.h>
+
+#include "oc_common.cuh"
+#include "conv_internal.cuh"
+
+namespace oc {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int sm_count() {
+  static thread_local int cached_dev = -1;
+  static thread_local int cached = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev != cached_dev) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) cached = n;
+    cached_dev = dev;
+  }
+  return cached;
+}
+
+struct ConvPlan {
+  bool tc;
+  size_t w_off, w_bytes, status_off, total;
+};
+
+static ConvPlan conv_plan(int K, int Cin, int Cout, int dtype) {
+  ConvPlan p;
+  p.tc = conv_tc_supported(K, Cin, Cout, dtype);
+  p.w_off = 0;
+  p.w_bytes = p.tc ? conv_tc_weight_bytes(K, Cin, Cout) : (size_t)K * Cin * Cout * sizeof(float);
+  p.status_off = align_up(p.w_bytes, 256);
+  p.total = p.status_off + 256;
+  return p;
+}
+
+struct WgradPlan {
+  bool tc;
+  int splits;
+  size_t partial_off, partial_bytes, stats_off, stats_bytes, total;
+};
+
+static WgradPlan wgrad_plan(int K, int Cin, int Cout, int64_t n_out, int dtype) {
+  WgradPlan p;
+  p.tc = wgrad_tc_supported(K, Cin, Cout, dtype);
+  p.splits = p.tc ? 0 : wgrad_fma_splits(K, Cin, Cout, n_out);
+  p.partial_off = 0;
+  p.partial_bytes = p.tc ? wgrad_tc_workspace_bytes(K, Cin, Cout, n_out)
+                         : (size_t)p.splits * K * Cin * Cout * sizeof(float);
+  p.stats_off = align_up(p.partial_bytes, 256);
+  p.stats_bytes = colstats_workspace_bytes(n_out, Cout);
+  p.total = p.stats_off + p.stats_bytes;
+  return p;
+}
+
+static int check_conv_common(const char* who, int K, int Cin, int Cout, int dtype, int idx_bytes,
+                             int table_cols, int64_t n_in, int64_t n_out) {
+  OC_REQUIRE(dtype == OC_F32 || dtype == OC_F16 || dtype == OC_BF16, OC_EINVAL, "%s: bad dtype %d", who, dtype);
+  OC_REQUIRE(K >= 1 && K <= OC_MAX_TAPS, OC_EINVAL, "%s: K %d not in [1,27]", who, K);
+  OC_REQUIRE(Cin >= 1 && Cout >= 1 && Cin <= 65536 && Cout <= 65536, OC_EINVAL, "%s: bad channels (%d, %d)", who, Cin, Cout);
+  OC_REQUIRE(idx_bytes == 8 || idx_bytes == 4, OC_EINVAL, "%s: idx_bytes must be 4 or 8", who);
+  OC_REQUIRE(table_cols >= 1 && table_cols <= 27, OC_EINVAL, "%s: table_cols %d not in [1,27]", who, table_cols);
+  OC_REQUIRE(n_in >= 0 && n_out >= 0 && n_in < (1LL << 31) && n_out < (1LL << 31), OC_EINVAL,
+             "%s: row counts must be in [0, 2^31)", who);
+  return OC_OK;
+}
+
+}  // namespace oc
+
+using namespace oc;
+
+extern "C" int oc_version(void) { return 100; }
+
+extern "C" const char* oc_last_error(void) { return g_err; }
+
+extern "C" size_t oc_conv_workspace_bytes(int K, int Cin, int Cout, int dtype) {
+  if (K < 1 || K > OC_MAX_TAPS || Cin < 1 || Cout < 1) return 0;
+  return conv_plan(K, Cin, Cout, dtype).total;
+}
+
+extern "C" int oc_conv_fwd(const void* data, int64_t n_in, const void* weights, int w_dtype,
+                           int w_transposed, const void* bias, const void* table, int idx_bytes,
+                           int table_cols, const int* h_taps, int K, int64_t n_out, int Cin,
+                           int Cout, int dtype, void* out, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+  int rc = check_conv_common("oc_conv_fwd", K, Cin, Cout, dtype, idx_bytes, table_cols, n_in, n_out);
+  if (rc) return rc;
+  OC_REQUIRE(w_dtype == OC_F32 || w_dtype == dtype, OC_EINVAL,
+             "oc_conv_fwd: weights must be fp32 or the data dtype");
+  ConvArgs a;
+  rc = make_taps(h_taps, K, table_cols, &a.taps, "oc_conv_fwd");
+  if (rc) return rc;
+  if (n_out == 0) return OC_OK;
+  OC_REQUIRE(weights && table && out && workspace, OC_EINVAL, "oc_conv_fwd: null pointer");
+  OC_REQUIRE(data || n_in == 0, OC_EINVAL, "oc_conv_fwd: null data");
+  const ConvPlan P = conv_plan(K, Cin, Cout, dtype);
+  OC_REQUIRE(workspace_bytes >= P.total, OC_ENOMEM, "oc_conv_fwd: workspace %zu < %zu bytes",
+             workspace_bytes, P.total);
+  a.data = data; a.n_in = n_in; a.bias = bias; a.table = table; a.idx_bytes = idx_bytes;
+  a.table_cols = table_cols; a.K = K; a.n_out = n_out; a.Cin = Cin; a.Cout = Cout; a.dtype = dtype;
+  a.out = out;
+  cudaStream_t s = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  if (P.tc) {
+    rc = prep_weights_tc(weights, w_dtype, K, Cin, Cout, w_transposed, dtype, ws + P.w_off, s);
+    if (rc) return rc;
+    return launch_conv_tc(a, ws + P.w_off, (int*)(ws + P.status_off), s);
+  }
+  rc = prep_weights_f32(weights, w_dtype, K, Cin, Cout, w_transposed, (float*)(ws + P.w_off), s);
+  if (rc) return rc;
+  return launch_conv_fma(a, (const float*)(ws + P.w_off), s);
+}
+
+extern "C" size_t oc_conv_wgrad_workspace_bytes(int K, int Cin, int Cout, int64_t n_out, int dtype) {
+  if (K < 1 || K > OC_MAX_TAPS || Cin < 1 || Cout < 1 || n_out < 0) return 0;
+  return wgrad_plan(K, Cin, Cout, n_out, dtype).total;
+}
+
+extern "C" int oc_conv_wgrad(const void* data, int64_t n_in, const void* grad_out, int64_t n_out,
+                             const void* table, int idx_bytes, int table_cols, const int* h_taps,
+                             int K, int Cin, int Cout, int dtype, float* grad_w, float* grad_bias,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_conv_common("oc_conv_wgrad", K, Cin, Cout, dtype, idx_bytes, table_cols, n_in, n_out);
+  if (rc) return rc;
+  WgradArgs a;
+  rc = make_taps(h_taps, K, table_cols, &a.taps, "oc_conv_wgrad");
+  if (rc) return rc;
+  OC_REQUIRE(grad_w, OC_EINVAL, "oc_conv_wgrad: null grad_w");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (n_out == 0) {
+    OC_CUDA_OK(cudaMemsetAsync(grad_w, 0, (size_t)K * Cin * Cout * 4, s));
+    if (grad_bias) OC_CUDA_OK(cudaMemsetAsync(grad_bias, 0, (size_t)Cout * 4, s));
+    return OC_OK;
+  }
+  OC_REQUIRE(grad_out && table && workspace, OC_EINVAL, "oc_conv_wgrad: null pointer");
+  OC_REQUIRE(data || n_in == 0, OC_EINVAL, "oc_conv_wgrad: null data");
+  const WgradPlan P = wgrad_plan(K, Cin, Cout, n_out, dtype);
+  OC_REQUIRE(workspace_bytes >= P.total, OC_ENOMEM, "oc_conv_wgrad: workspace %zu < %zu bytes",
+             workspace_bytes, P.total);
+  a.data = data; a.n_in = n_in; a.grad_out = grad_out; a.n_out = n_out; a.table = table;
+  a.idx_bytes = idx_bytes; a.table_cols = table_cols; a.K = K; a.Cin = Cin; a.Cout = Cout; a.dtype = dtype;
+  char* ws = (char*)workspace;
+  if (P.tc) {
+    rc = launch_wgrad_tc(a, grad_w, ws + P.partial_off, P.partial_bytes, s);
+  } else {
+    rc = launch_wgrad_fma(a, (float*)(ws + P.partial_off), P.splits, s);
+    if (rc) return rc;
+    rc = reduce_partials((const float*)(ws + P.partial_off), P.splits, (int64_t)K * Cin * Cout, grad_w, s);
+  }
+  if (rc) return rc;
+  if (grad_bias)
+    rc = launch_colstats(grad_out, nullptr, n_out, Cout, dtype, grad_bias, nullptr, ws + P.stats_off,
+                         P.stats_bytes, s);
+  return rc;
+}
