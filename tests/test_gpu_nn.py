@@ -1,0 +1,276 @@
+"""GPU parity of the octree operators against the reference's golden outputs and
+the numpy oracle.  Tolerances (relative L2 and max-norm, both must hold):
+fp32 1e-4; fp16 / bf16 1e-2 against an fp32 computation on the same rounded
+inputs.  Integer outputs (pool indices) and pure copies must be equal."""
+import numpy as np
+import pytest
+import torch
+
+import ocnn_pytorch_b200 as b200
+from oracle import octree_oracle as orc
+from helpers import assert_close, conv_case, octree_from_golden
+from gpu_utils import dev, to_np, build, synthetic_octree
+
+pytestmark = pytest.mark.gpu
+
+TOL32 = 1e-4
+TOL16 = 1e-2
+
+
+def T(a, dtype=torch.float32, grad=False):
+  t = torch.from_numpy(np.ascontiguousarray(a)).to(dev()).to(dtype)
+  return t.requires_grad_() if grad else t
+
+
+@pytest.fixture(scope='module')
+def syn_octree(golden):
+  octree, _ = synthetic_octree(golden['synthetic'])
+  return octree
+
+
+def _make(c):
+  cls = b200.nn.OctreeConv if c['op'] == 'conv' else b200.nn.OctreeDeconv
+  m = cls(c['cin'], c['cout'], c['kernel_size'], c['stride'], c['nempty'], use_bias=c['use_bias']).to(dev())
+  with torch.no_grad():
+    m.weights.copy_(T(c['w']))
+    if c['use_bias']:
+      m.bias.copy_(T(c['b']))
+  return m
+
+
+def test_conv_deconv_golden_fp32(golden, syn_octree):
+  syn = golden['synthetic']
+  for ci in range(int(syn['n_conv_cases'])):
+    c = conv_case(syn, ci)
+    m = _make(c)
+    x = T(c['x'], grad=True)
+    y = m(x, syn_octree, c['depth'])
+    y.backward(T(c['gy']))
+    what = 'case %d %s k%s s%d ne%d' % (ci, c['op'], c['kernel'], c['stride'], c['nempty'])
+    assert_close(to_np(y), c['y'], TOL32, what + ' y')
+    assert_close(to_np(x.grad), c['gx'], TOL32, what + ' gx')
+    assert_close(to_np(m.weights.grad), c['gw'], TOL32, what + ' gw')
+    if c['use_bias']:
+      assert_close(to_np(m.bias.grad), c['gb'], TOL32, what + ' gb')
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_conv_deconv_golden_half(golden, syn_octree, dtype):
+  # inputs rounded to the half type; expectation = oracle in fp32 on the rounded values
+  syn = golden['synthetic']
+  keys, children, neighs = octree_from_golden(syn)
+  from test_oracle import _conv_oracle
+  for ci in range(int(syn['n_conv_cases'])):
+    c = conv_case(syn, ci)
+    rnd = lambda a: to_np(T(a, dtype))
+    c2 = dict(c)
+    for k in ('x', 'w', 'gy') + (('b',) if c['use_bias'] else ()):
+      c2[k] = rnd(c[k])
+    ey, egx, egw, egb = _conv_oracle(c2, children, neighs)
+    m = _make(c).to(dtype)
+    x = T(c['x'], dtype, grad=True)
+    y = m(x, syn_octree, c['depth'])
+    assert y.dtype == dtype
+    y.backward(T(c['gy'], dtype))
+    what = '%s case %d %s k%s s%d ne%d' % (dtype, ci, c['op'], c['kernel'], c['stride'], c['nempty'])
+    assert_close(to_np(y), ey, TOL16, what + ' y')
+    assert_close(to_np(x.grad), egx, TOL16, what + ' gx')
+    assert_close(to_np(m.weights.grad), egw, TOL16, what + ' gw')
+    if c['use_bias']:
+      assert_close(to_np(m.bias.grad), egb, TOL16, what + ' gb')
+
+
+def _oracle_conv333(octree_np, x, w, gy, nempty, d):
+  neigh = orc.get_neigh(octree_np['neighs'][d], octree_np['children'][d], '333', 1, nempty)
+  y = orc.conv_forward(x, w, neigh)
+  return y, orc.conv_backward(gy, w, neigh, x.shape[0]), orc.conv_weight_grad(x, gy, neigh)
+
+
+@pytest.fixture(scope='module')
+def mid_octree():
+  # 2 octrees, depth 6, 20k points each: the reference's CPU-runnable configuration
+  B, n, depth, fd = 2, 20000, 6, 2
+  clouds = [b200.synthetic.spheres_cloud(1000 + i, n) for i in range(B)]
+  pts = np.concatenate([c[0] for c in clouds])
+  nrm = np.concatenate([c[1] for c in clouds])
+  bid = np.concatenate([np.full(n, i, np.float32) for i in range(B)])
+  octree, _ = build(pts, nrm, None, bid, B, depth, fd)
+  o = orc.build_octree(pts, nrm, None, bid, B, depth, fd)
+  o['neighs'] = orc.construct_all_neigh(o['children'], o['nnum'], depth, fd, B)
+  return octree, o
+
+
+@pytest.mark.parametrize('cin,cout', [(32, 32), (1, 3), (4, 32), (30, 69), (64, 64), (96, 128),
+                                      (133, 16), (256, 64), (16, 272)])
+@pytest.mark.parametrize('nempty', [False, True])
+def test_conv333_vs_oracle_fp32(mid_octree, cin, cout, nempty):
+  octree, o = mid_octree
+  d = 5 if cin * cout > 64 * 64 else 6
+  rng = np.random.default_rng(cin * 1000 + cout)
+  n = int(o['nnum_nempty'][d] if nempty else o['nnum'][d])
+  x = rng.standard_normal((n, cin)).astype(np.float32)
+  w = (rng.standard_normal((27, cin, cout)) / np.sqrt(27 * cin)).astype(np.float32)
+  gy = rng.standard_normal((n, cout)).astype(np.float32)
+  ey, egx, egw = _oracle_conv333(o, x, w, gy, nempty, d)
+  m = b200.nn.OctreeConv(cin, cout, [3], 1, nempty).to(dev())
+  with torch.no_grad():
+    m.weights.copy_(T(w))
+  xt = T(x, grad=True)
+  y = m(xt, octree, d)
+  y.backward(T(gy))
+  assert_close(to_np(y), ey, TOL32, 'y')
+  assert_close(to_np(xt.grad), egx, TOL32, 'gx')
+  assert_close(to_np(m.weights.grad), egw, TOL32, 'gw')
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('cin,cout', [(32, 32), (64, 64), (16, 48), (96, 96), (128, 128), (64, 128),
+                                      (128, 64), (256, 256), (384, 256), (192, 128), (32, 272),
+                                      (4, 32), (69, 133)])
+@pytest.mark.parametrize('nempty', [False, True])
+def test_conv333_vs_oracle_half(mid_octree, cin, cout, nempty, dtype):
+  octree, o = mid_octree
+  d = 5 if cin * cout > 64 * 64 else 6
+  rng = np.random.default_rng(cin * 1000 + cout + 7)
+  n = int(o['nnum_nempty'][d] if nempty else o['nnum'][d])
+  rnd = lambda a: to_np(T(a, dtype))
+  x = rnd(rng.standard_normal((n, cin)).astype(np.float32))
+  w = rnd((rng.standard_normal((27, cin, cout)) / np.sqrt(27 * cin)).astype(np.float32))
+  gy = rnd(rng.standard_normal((n, cout)).astype(np.float32))
+  ey, egx, egw = _oracle_conv333(o, x, w, gy, nempty, d)
+  m = b200.nn.OctreeConv(cin, cout, [3], 1, nempty).to(dev()).to(dtype)
+  with torch.no_grad():
+    m.weights.copy_(T(w, dtype))
+  xt = T(x, dtype, grad=True)
+  y = m(xt, octree, d)
+  y.backward(T(gy, dtype))
+  assert_close(to_np(y), ey, TOL16, 'y')
+  assert_close(to_np(xt.grad), egx, TOL16, 'gx')
+  assert_close(to_np(m.weights.grad), egw, TOL16, 'gw')
+
+
+def test_conv_is_deterministic_and_linear(mid_octree):
+  octree, o = mid_octree
+  d, C = 6, 64
+  n = int(o['nnum'][d])
+  g = torch.Generator(device=dev()).manual_seed(1)
+  m = b200.nn.OctreeConv(C, C).to(dev()).half()
+  x1 = torch.randn(n, C, device=dev(), generator=g).half()
+  x2 = torch.randn(n, C, device=dev(), generator=g).half()
+  y1, y1b = m(x1, octree, d), m(x1, octree, d)
+  assert torch.equal(y1, y1b)                         # no atomics anywhere: bitwise repeatable
+  y2 = m(x2, octree, d)
+  y12 = m((x1.float() + x2.float()).half(), octree, d)
+  assert_close(to_np(y12), to_np(y1.float() + y2.float()), TOL16, 'linearity')
+
+
+def test_dwconv_golden(golden, syn_octree):
+  syn = golden['synthetic']
+  for ci in range(int(syn['n_dw_cases'])):
+    t = 'd%02d' % ci
+    stride, nempty, C = int(syn[t + '_meta'][0]), bool(syn[t + '_meta'][1]), int(syn[t + '_meta'][2])
+    ks = [int(v) for v in syn[t + '_meta'][3:6]]
+    m = b200.nn.OctreeDWConv(C, ks, stride, nempty).to(dev())
+    with torch.no_grad():
+      m.weights.copy_(T(syn[t + '_w']))
+    x = T(syn[t + '_x'], grad=True)
+    y = m(x, syn_octree, 4)
+    y.backward(T(syn[t + '_gy']))
+    assert_close(to_np(y), syn[t + '_y'], TOL32, t + ' y')
+    assert_close(to_np(x.grad), syn[t + '_gx'], TOL32, t + ' gx')
+    assert_close(to_np(m.weights.grad), syn[t + '_gw'], TOL32, t + ' gw')
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+def test_dwconv_equals_single_channel_convs(mid_octree, dtype):
+  # structure of the reference's test/test_octree_dwconv.py:18-55
+  octree, o = mid_octree
+  d, C = 5, 8
+  n = int(o['nnum'][d])
+  g = torch.Generator(device=dev()).manual_seed(3)
+  x = torch.randn(n, C, device=dev(), generator=g).to(dtype)
+  dw = b200.nn.OctreeDWConv(C, [3]).to(dev())
+  y = dw(x, octree, d)
+  for c in range(C):
+    conv = b200.nn.OctreeConv(1, 1, [3]).to(dev())
+    with torch.no_grad():
+      conv.weights.copy_(dw.weights[:, :, c:c + 1])
+    yc = conv(x[:, c:c + 1].contiguous(), octree, d)
+    assert_close(to_np(y[:, c:c + 1]), to_np(yc), 1e-5 if dtype == torch.float32 else TOL16, 'channel %d' % c)
+
+
+def test_pool_upsample_pad_golden(golden, syn_octree):
+  syn = golden['synthetic']
+  for ne in (0, 1):
+    for dtype in (torch.float32, torch.float16):
+      x = T(syn['p%d_x' % ne], dtype, grad=True)
+      y, ind = b200.nn.octree_max_pool(x, syn_octree, 5, bool(ne), return_indices=True)
+      y.backward(T(syn['p%d_gy' % ne], dtype))
+      if dtype == torch.float32:
+        assert np.array_equal(to_np(y), syn['p%d_y' % ne])
+        assert np.array_equal(to_np(x.grad), syn['p%d_gx' % ne])
+        assert np.array_equal(to_np(ind), syn['p%d_ind' % ne].astype(np.int64))
+        un = b200.nn.octree_max_unpool(y.detach(), ind, syn_octree, 4, bool(ne))
+        assert un.shape == x.shape
+        assert torch.equal(un != 0, (x.grad != 0) | ((un != 0) & (x.grad == 0)))
+      else:
+        ey, eind = orc.max_pool(to_np(x), to_np(syn_octree.children[5]), to_np(syn_octree.children[4]), bool(ne))
+        assert np.array_equal(to_np(y), ey)
+      u = T(syn['u%d_x' % ne], dtype, grad=True)
+      up = b200.nn.octree_nearest_upsample(u, syn_octree, 4, bool(ne))
+      up.backward(T(syn['u%d_gy' % ne], dtype))
+      if dtype == torch.float32:
+        assert np.array_equal(to_np(up), syn['u%d_y' % ne])
+        assert_close(to_np(u.grad), syn['u%d_gx' % ne], 1e-6, 'upsample grad')
+      mod = b200.nn.OctreeUpsample('nearest', bool(ne))
+      assert torch.equal(mod(u.detach(), syn_octree, 4), up.detach())
+  pad = b200.nn.octree_pad(T(syn['pad_x']), syn_octree, 5, 1.5)
+  assert np.array_equal(to_np(pad), syn['pad_y'])
+  assert np.array_equal(to_np(b200.nn.octree_depad(pad, syn_octree, 5)), syn['depad_y'])
+  # odd channel count / half type take the scalar path
+  x = torch.randn(int(syn_octree.nnum_nempty[5]), 5, device=dev()).half()
+  p = b200.nn.octree_pad(x, syn_octree, 5)
+  assert torch.equal(b200.nn.octree_depad(p, syn_octree, 5), x)
+
+
+def test_norms_golden(golden, syn_octree):
+  syn = golden['synthetic']
+  for ni in range(3):
+    t = 'g%d' % ni
+    C, group, nempty = (int(v) for v in syn[t + '_meta'])
+    m = b200.nn.OctreeGroupNorm(C, group, bool(nempty), min_group_channels=1).to(dev())
+    with torch.no_grad():
+      m.weights.copy_(T(syn[t + '_w']))
+      m.bias.copy_(T(syn[t + '_b']))
+    x = T(syn[t + '_x'], grad=True)
+    y = m(x, syn_octree, 5)
+    y.backward(T(syn[t + '_gy']))
+    assert np.allclose(to_np(y), syn[t + '_y'], atol=5e-6), t
+    assert np.allclose(to_np(x.grad), syn[t + '_gx'], atol=2e-5), t
+    assert np.allclose(to_np(m.weights.grad), syn[t + '_gw'], rtol=1e-4, atol=1e-3), t
+    assert np.allclose(to_np(m.bias.grad), syn[t + '_gb'], rtol=1e-4, atol=1e-3), t
+  bn = b200.nn.OctreeBatchNorm(9).to(dev())
+  with torch.no_grad():
+    bn.weight.copy_(T(syn['bn_w']))
+    bn.bias.copy_(T(syn['bn_b']))
+  x = T(syn['bn_x'], grad=True)
+  y = bn(x)
+  y.backward(T(syn['bn_gy']))
+  assert np.allclose(to_np(y), syn['bn_y'], atol=5e-6)
+  assert np.allclose(to_np(x.grad), syn['bn_gx'], atol=5e-6)
+  assert np.allclose(to_np(bn.weight.grad), syn['bn_gw'], rtol=1e-4, atol=1e-3)
+  assert np.allclose(to_np(bn.bias.grad), syn['bn_gb'], rtol=1e-4, atol=1e-3)
+  assert np.allclose(to_np(bn.running_mean), syn['bn_rm'], atol=1e-6)
+  assert np.allclose(to_np(bn.running_var), syn['bn_rv'], atol=1e-5)
+  bn.eval()
+  assert np.allclose(to_np(bn(x.detach())), syn['bn_y_eval'], atol=5e-6)
+
+
+def test_conv_error_paths(syn_octree):
+  m = b200.nn.OctreeConv(4, 8).to(dev())
+  with pytest.raises(AssertionError):
+    m(torch.zeros(3, 4, device=dev()), syn_octree, 5)               # wrong row count
+  with pytest.raises(ValueError):
+    b200.nn.OctreeConv(4, 8, [4]).to(dev())(torch.zeros(int(syn_octree.nnum[5]), 4, device=dev()), syn_octree, 5)
+  with pytest.raises(TypeError):
+    m.double()(torch.zeros(int(syn_octree.nnum[5]), 4, device=dev(), dtype=torch.float64), syn_octree, 5)
