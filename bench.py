@@ -1,0 +1,345 @@
+"""Benchmark of the octree-convolution hot path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+A step = OctreeConv 3x3x3 stride-1 forward + backward (input and weight
+gradients) over one batch of 16 depth-8 octrees (100k surface points each),
+Cin = Cout = 64, fp16 — the conv micro-benchmark configuration.  Every rank owns
+its own batch (weak scaling, no collective on the path).  One JSON line is
+printed by rank 0.
+
+--impl reference times the CPU restatement of the reference's gather-GEMM
+(oracle/, numpy, all host threads) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = 'octree_conv_fwd_bwd_tflops'
+UNIT = 'TFLOP/s'
+DEPTH, FULL_DEPTH, BATCH, NPTS, CH = 8, 3, 16, 100000, 64
+CONFIG_ID = 2
+
+
+def workload_clouds(rank=0, batch=BATCH, npts=NPTS):
+  import ocnn_pytorch_b200 as b200
+  clouds = [b200.synthetic.mixed_cloud(1000 * CONFIG_ID + 100 * rank + i, npts) for i in range(batch)]
+  pts = np.concatenate([c[0] for c in clouds])
+  nrm = np.concatenate([c[1] for c in clouds])
+  bid = np.concatenate([np.full(npts, i, np.float32) for i in range(batch)])
+  return pts, nrm, bid
+
+
+def peaks():
+  path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+  if os.path.exists(path):
+    p = json.load(open(path))
+    return dict(tflops=float(p['bf16_tflops']), tflops_sustained=float(p.get('bf16_tflops_sustained', p['bf16_tflops'])),
+                hbm=float(p['hbm_gbs']), src='measured')
+  return dict(tflops=1590.0, tflops_sustained=1400.0, hbm=6650.0, src='fallback')
+
+
+class ClockSampler:
+  """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+  def __init__(self, index=0):
+    self.index = index
+    self.rows = []
+    self.proc = None
+
+  def __enter__(self):
+    q = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,'
+         'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+         'clocks_event_reasons.sw_power_cap')
+    try:
+      self.proc = subprocess.Popen(['nvidia-smi', '-i', str(self.index), '--query-gpu=' + q,
+                                    '--format=csv,noheader,nounits', '-lms', '100'],
+                                   stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+      self.thread = threading.Thread(target=self._read, daemon=True)
+      self.thread.start()
+    except Exception:
+      self.proc = None
+    return self
+
+  def _read(self):
+    for line in self.proc.stdout:
+      self.rows.append([c.strip() for c in line.split(',')])
+
+  def __exit__(self, *a):
+    if self.proc is not None:
+      time.sleep(0.15)
+      self.proc.terminate()
+      try:
+        self.proc.wait(timeout=5)
+      except Exception:
+        self.proc.kill()
+
+  def summary(self):
+    sm, mx, reasons = [], [], set()
+    names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+    for r in self.rows:
+      try:
+        sm.append(float(r[0]))
+        mx.append(float(r[1]))
+      except Exception:
+        continue
+      for n, v in zip(names, r[2:6]):
+        if v.lower().startswith('active'):
+          reasons.add(n)
+    if not sm:
+      return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': [], 'samples': 0}
+    return {'sm_mhz': float(np.median(sm)), 'sm_max_mhz': float(max(mx)), 'reasons': sorted(reasons),
+            'samples': len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_conv_sample(n_octrees=1, channels=CH, threads=None):
+  """Builds `n_octrees` octrees of the workload with the oracle and returns a
+  closure running conv forward + backward (fp32, numpy) plus its work figures."""
+  from oracle import octree_oracle as orc
+  pts, nrm, bid = workload_clouds(0, n_octrees)
+  o = orc.build_octree(pts, nrm, None, bid, n_octrees, DEPTH, FULL_DEPTH)
+  neighs = orc.construct_all_neigh(o['children'], o['nnum'], DEPTH, FULL_DEPTH, n_octrees)
+  neigh = neighs[DEPTH]
+  n = neigh.shape[0]
+  rng = np.random.default_rng(0)
+  x = rng.standard_normal((n, channels)).astype(np.float32)
+  gy = rng.standard_normal((n, channels)).astype(np.float32)
+  w = (rng.standard_normal((27, channels, channels)) / np.sqrt(27 * channels)).astype(np.float32)
+  nnz = int((neigh >= 0).sum())
+
+  def step():
+    y = orc.conv_forward(x, w, neigh)
+    gx = orc.conv_backward(gy, w, neigh, n)
+    gw = orc.conv_weight_grad(x, gy, neigh)
+    return float(y[0, 0] + gx[0, 0] + gw[0, 0, 0])
+  return step, n, nnz
+
+
+def run_reference(args):
+  rank = int(os.environ.get('RANK', '0'))
+  if rank != 0:
+    return
+  cores = os.cpu_count() or 1
+  step, n, nnz = cpu_conv_sample(1)
+  for _ in range(max(args.warmup, 0) and 1):
+    step()
+  t0 = time.perf_counter()
+  for _ in range(args.steps):
+    step()
+  dt = (time.perf_counter() - t0) / args.steps
+  flops = 3 * 2.0 * nnz * CH * CH
+  val = flops / dt / 1e12
+  sample = '1 of %d octrees (depth %d, %d rows, %d valid taps), fp32 numpy gather-GEMM fwd+dgrad+wgrad' % (
+      BATCH, DEPTH, n, nnz)
+  line = {
+      'impl': 'reference', 'metric': METRIC, 'value': val, 'unit': UNIT, 'n_gpus': args.gpus,
+      'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': dt * 1e3, 'higher_is_better': True,
+      'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+      'config': workload_config(),
+      'cpu_baseline': {'value': val, 'unit': UNIT, 'cores': cores, 'kind': 'port', 'sample': sample},
+      'e2e': {'value': val, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+  }
+  print(json.dumps(line))
+
+
+def workload_config():
+  return {'workload': 'OctreeConv 3x3x3 s1 fwd+bwd, 16 octrees depth 8 (full_depth 3) x 100k surface '
+                      'points, Cin=Cout=64, nempty=False',
+          'l2': 'inputs (features + neighbour table, >600 MB) exceed the 126 MB L2',
+          'flops': 'valid taps only: 3 passes x 2*nnz*Cin*Cout'}
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+  import torch
+  import torch.distributed as dist
+  import ocnn_pytorch_b200 as b200
+
+  rank = int(os.environ.get('RANK', '0'))
+  local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+  world = int(os.environ.get('WORLD_SIZE', '1'))
+  if not torch.cuda.is_available():
+    raise SystemExit('bench.py needs a CUDA device: the hot path has no CPU fallback')
+  torch.cuda.set_device(local_rank)
+  dev = torch.device('cuda', local_rank)
+  if world > 1:
+    os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+
+  # ---- the batch of this rank (weak scaling: every rank has a full batch)
+  pts, nrm, bid = workload_clouds(rank)
+  h_pts = torch.from_numpy(pts).pin_memory()
+  h_nrm = torch.from_numpy(nrm).pin_memory()
+  h_bid = torch.from_numpy(bid).pin_memory()
+
+  def build_octree():
+    pc = b200.Points(h_pts.to(dev, non_blocking=True), h_nrm.to(dev, non_blocking=True),
+                     batch_id=h_bid.to(dev, non_blocking=True), batch_size=BATCH)
+    octree = b200.Octree(DEPTH, FULL_DEPTH, BATCH, dev)
+    octree.build_octree(pc)
+    octree.construct_all_neigh()
+    return octree
+
+  octree = build_octree()
+  torch.cuda.synchronize()
+  # octree build throughput (secondary figure): host points -> octree + all neighbour tables
+  t_build = []
+  for i in range(3):
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    o2 = build_octree()
+    torch.cuda.synchronize()
+    t_build.append(time.perf_counter() - t0)
+    del o2
+  build_mpts = BATCH * NPTS / min(t_build) / 1e6
+
+  n = int(octree.nnum[DEPTH])
+  neigh = octree.neighs[DEPTH]
+  nnz = int((neigh >= 0).sum().item())
+  flops_valid = 3 * 2.0 * nnz * CH * CH
+  flops_dense = 3 * 2.0 * n * 27 * CH * CH
+
+  g = torch.Generator(device=dev).manual_seed(rank)
+  conv = b200.nn.OctreeConv(CH, CH, [3], 1, False).to(dev).half()
+  x = torch.randn(n, CH, device=dev, generator=g).half().requires_grad_()
+  gy = torch.randn(n, CH, device=dev, generator=g).half()
+
+  def step():
+    conv.weights.grad = None
+    x.grad = None
+    y = conv(x, octree, DEPTH)
+    y.backward(gy)
+    return y
+
+  def barrier():
+    if world > 1:
+      dist.barrier()
+    torch.cuda.synchronize()
+
+  for _ in range(max(args.warmup, 3)):
+    step()
+  barrier()
+  ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  with ClockSampler(local_rank) as clocks:
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+      step()
+    ev1.record()
+    barrier()
+  ms = ev0.elapsed_time(ev1) / args.steps
+  if world > 1:
+    t = torch.tensor([ms], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+
+  # ---- dominant kernel alone: the gather implicit GEMM (forward launch)
+  table, taps = octree.conv_table(DEPTH, '333', 1, False)
+  xd = x.detach()
+  reps = max(args.steps, 5)
+  for _ in range(3):
+    b200.nn.conv_gather(xd, conv.weights, False, None, table, taps, CH, CH)
+  torch.cuda.synchronize()
+  k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  k0.record()
+  for _ in range(reps):
+    b200.nn.conv_gather(xd, conv.weights, False, None, table, taps, CH, CH)
+  k1.record()
+  torch.cuda.synchronize()
+  ms_fwd = k0.elapsed_time(k1) / reps
+
+  # ---- end to end: host buffers in, host buffers out, through the module API
+  h_x = x.detach().cpu().pin_memory()
+  h_gy = gy.cpu().pin_memory()
+  h_y = torch.empty(n, CH, dtype=torch.float16).pin_memory()
+  h_gx = torch.empty(n, CH, dtype=torch.float16).pin_memory()
+  h_gw = torch.empty(27, CH, CH, dtype=torch.float32).pin_memory()
+
+  def e2e_step():
+    xd2 = h_x.to(dev, non_blocking=True).requires_grad_()
+    gyd = h_gy.to(dev, non_blocking=True)
+    conv.weights.grad = None
+    y = conv(xd2, octree, DEPTH)
+    y.backward(gyd)
+    h_y.copy_(y.detach(), non_blocking=True)
+    h_gx.copy_(xd2.grad, non_blocking=True)
+    h_gw.copy_(conv.weights.grad.float(), non_blocking=True)
+
+  for _ in range(3):
+    e2e_step()
+  barrier()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for _ in range(args.steps):
+    e2e_step()
+  e1.record()
+  barrier()
+  ms_e2e = e0.elapsed_time(e1) / args.steps
+  if world > 1:
+    t = torch.tensor([ms_e2e], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_e2e = float(t.item())
+  h2d = h_x.numel() * 2 + h_gy.numel() * 2
+  d2h = h_y.numel() * 2 + h_gx.numel() * 2 + h_gw.numel() * 4
+
+  pk = peaks()
+  fwd_flops = 2.0 * nnz * CH * CH
+  achieved = fwd_flops / (ms_fwd * 1e-3) / 1e12
+  line = {
+      'metric': METRIC, 'value': world * flops_valid / (ms * 1e-3) / 1e12, 'unit': UNIT,
+      'n_gpus': world, 'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms,
+      'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f16',
+      'data': 'synthetic', 'config': workload_config(),
+      'rows': n, 'valid_taps': nnz, 'dense_equiv_tflops': world * flops_dense / (ms * 1e-3) / 1e12,
+      'ms_fwd_kernel': ms_fwd, 'build': {'mpts_per_s': build_mpts, 'points': BATCH * NPTS,
+                                         'what': 'pinned host points -> octree + neighbour tables, depth 8'},
+      'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': pk['tflops'], 'unit': 'TFLOP/s',
+                   'frac': achieved / pk['tflops'], 'traffic': None,
+                   'kernel': 'conv gather implicit GEMM (forward launch), valid-tap FLOPs', 'peak_src': pk['src']},
+      'e2e': {'value': world * flops_valid / (ms_e2e * 1e-3) / 1e12, 'unit': UNIT,
+              'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h, 'ms_per_step': ms_e2e},
+      'gpu_launches': 6 * args.steps,
+      'clocks': clocks.summary(),
+  }
+  if rank == 0 and world == 1:
+    t0 = time.perf_counter()
+    cstep, cn, cnnz = cpu_conv_sample(1)
+    cstep()
+    t1 = time.perf_counter()
+    cstep()
+    dt = time.perf_counter() - t1
+    line['cpu_baseline'] = {
+        'value': 3 * 2.0 * cnnz * CH * CH / dt / 1e12, 'unit': UNIT, 'cores': os.cpu_count() or 1,
+        'kind': 'port', 'sample': '1 of %d octrees (%d rows), fp32 numpy gather-GEMM fwd+dgrad+wgrad, %.1f s' % (
+            BATCH, cn, dt)}
+  if rank == 0:
+    print(json.dumps(line))
+  if world > 1:
+    dist.destroy_process_group()
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument('--gpus', type=int, default=1)
+  ap.add_argument('--steps', type=int, default=20)
+  ap.add_argument('--warmup', type=int, default=5)
+  ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+  args = ap.parse_args()
+  if args.impl == 'reference':
+    run_reference(args)
+  else:
+    run_ours(args)
+
+
+if __name__ == '__main__':
+  main()

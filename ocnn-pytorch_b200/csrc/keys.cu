@@ -54,7 +54,7 @@ using namespace oc;
 
 extern "C" int oc_xyz2key(const void* x, const void* y, const void* z, const void* b,
                           int coord_dtype, int64_t n, int depth, int64_t* key, void* stream) {
-  OC_REQUIRE(depth >= 1 && depth <= 16, OC_EINVAL, "oc_xyz2key: depth %d not in [1,16]", depth);
+  OC_REQUIRE(depth >= 0 && depth <= 16, OC_EINVAL, "oc_xyz2key: depth %d not in [0,16]", depth);
   OC_REQUIRE(n >= 0, OC_EINVAL, "oc_xyz2key: negative n");
   if (n == 0) return OC_OK;
   OC_REQUIRE(x && y && z && key, OC_EINVAL, "oc_xyz2key: null pointer");
@@ -90,7 +90,7 @@ extern "C" int oc_xyz2key(const void* x, const void* y, const void* z, const voi
 
 extern "C" int oc_key2xyz(const int64_t* key, int64_t n, int depth, int64_t* x, int64_t* y,
                           int64_t* z, int64_t* b, void* stream) {
-  OC_REQUIRE(depth >= 1 && depth <= 16, OC_EINVAL, "oc_key2xyz: depth %d not in [1,16]", depth);
+  OC_REQUIRE(depth >= 0 && depth <= 16, OC_EINVAL, "oc_key2xyz: depth %d not in [0,16]", depth);
   OC_REQUIRE(n >= 0, OC_EINVAL, "oc_key2xyz: negative n");
   if (n == 0) return OC_OK;
   OC_REQUIRE(key && x && y && z, OC_EINVAL, "oc_key2xyz: null pointer");

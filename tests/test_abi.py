@@ -48,7 +48,7 @@ def test_argument_errors_need_no_gpu():
   assert lib.oc_build_workspace_bytes(1000, 6, 2, 1) > 0
   assert lib.oc_build_workspace_bytes(1000, 99, 2, 1) == 0
   with pytest.raises(_lib.OctConvError):
-    _lib.call('oc_key2xyz', None, 5, 0, None, None, None, None, None)
+    _lib.call('oc_key2xyz', None, 5, 17, None, None, None, None, None)
 
 
 def test_cpu_tensors_are_rejected_loudly():
