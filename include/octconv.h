@@ -48,6 +48,12 @@ enum { OC_I64 = 10, OC_I32 = 11, OC_COORD_F32 = 12, OC_COORD_F64 = 13, OC_I16 = 
 int oc_version(void);
 const char* oc_last_error(void);
 
+/* Device-side waits in the tensor-core kernels are bounded; a wait that expires
+ * makes the kernel unwind and sets a sticky per-device status word.  This call
+ * synchronises `stream`, returns OC_ETIMEOUT if the word is set (and clears it),
+ * OC_OK otherwise.  No counterpart in the reference (its kernels cannot time out). */
+int oc_status_check(void* stream);
+
 /* ---- Morton ("shuffled") keys ------------------------------------------- */
 
 /* ocnn/octree/shuffled_key.py:60-90 (xyz2key).  x,y,z (and b, may be NULL) are

@@ -26,6 +26,7 @@ _vpp = ctypes.POINTER(ctypes.c_void_p)
 PROTOTYPES = {
     'oc_version': (_i, []),
     'oc_last_error': (ctypes.c_char_p, []),
+    'oc_status_check': (_i, [_vp]),
     'oc_xyz2key': (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i, _vp, _vp]),
     'oc_key2xyz': (_i, [_vp, _i64, _i, _vp, _vp, _vp, _vp, _vp]),
     'oc_build_workspace_bytes': (_sz, [_i64, _i, _i, _i]),
@@ -100,6 +101,11 @@ def check(status, what=''):
 def call(name, *args):
   """Calls entry point `name` and raises OctConvError on a non-zero status."""
   check(getattr(lib(), name)(*args), name)
+
+
+def status_check(device=None):
+  """Synchronises the current stream and raises if a tensor-core kernel abandoned a wait."""
+  call('oc_status_check', stream(device))
 
 
 def ptr(t):

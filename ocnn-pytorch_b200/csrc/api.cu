@@ -83,6 +83,16 @@ extern "C" int oc_version(void) { return 100; }
 
 extern "C" const char* oc_last_error(void) { return g_err; }
 
+extern "C" int oc_status_check(void* stream) {
+  int v = 0;
+  int rc = read_tc_status((cudaStream_t)stream, &v);
+  if (rc) return rc;
+  OC_REQUIRE(v == 0, OC_ETIMEOUT,
+             "a bounded device-side wait expired in a tensor-core kernel (role code %d); results of "
+             "kernels launched since the last check are invalid", v);
+  return OC_OK;
+}
+
 extern "C" size_t oc_conv_workspace_bytes(int K, int Cin, int Cout, int dtype) {
   if (K < 1 || K > OC_MAX_TAPS || Cin < 1 || Cout < 1) return 0;
   return conv_plan(K, Cin, Cout, dtype).total;

@@ -48,6 +48,8 @@ int prep_weights_tc(const void* w, int w_dtype, int K, int Cin, int Cout, int tr
                     void* out, cudaStream_t s);
 int launch_conv_tc(const ConvArgs& a, const void* Wimg, int* status_dev, cudaStream_t s);
 
+int read_tc_status(cudaStream_t s, int* h_status);
+
 bool wgrad_tc_supported(int K, int Cin, int Cout, int dtype);
 size_t wgrad_tc_workspace_bytes(int K, int Cin, int Cout, int64_t n_out);
 int launch_wgrad_tc(const WgradArgs& a, float* grad_w, void* workspace, size_t workspace_bytes,

@@ -1,12 +1,461 @@
-// placeholder; replaced by the tcgen05 implementation
+// Octree convolution on the 5th-generation tensor cores (tcgen05 + TMEM), fp16 /
+// bf16 data with fp32 accumulation.
+//
+// Gather implicit GEMM (forward, and input gradient through a mirrored / inverse
+// table): out[r, :] = sum_k data[table[r, taps[k]], :] . Wk.  It replaces the
+// reference's Triton kernels conv_fwd_implicit_gemm(_splitk) and
+// conv_bwd_input_implicit_gemm(_splitk) (ocnn/nn/kernels/*.py) and the im2col +
+// torch.mm path of ocnn/nn/octree_conv.py:115-168.
+//
+// One persistent CTA per SM walks 128-row output tiles.  Warp roles:
+//   warps 0-3  epilogue : TMEM -> registers -> (+bias, cast) -> global
+//   warps 4-7  producers: stage = (tap, 64-channel block).  A operand: the 128
+//                         gathered input rows, copied by cp.async (16 B per lane,
+//                         8 lanes per row, zero-fill for missing neighbours) into
+//                         the 128-byte-swizzled K-major layout the MMA reads.
+//                         B operand: the matching block of the pre-swizzled weight
+//                         image, one bulk copy.  Taps with no valid neighbour in
+//                         the whole tile are skipped (warp-OR of the index signs).
+//   warp 8     MMA issuer: tcgen05.mma 128 x Cout x 16 per K step, accumulators
+//                         double-buffered in TMEM so the epilogue of tile i
+//                         overlaps the main loop of tile i+1.
+// Stages flow through a ring of full/empty mbarriers; a per-stage header tells
+// the MMA warp whether the stage starts or ends a tile.  Every wait is bounded.
 #include "oc_common.cuh"
 #include "conv_internal.cuh"
+#include "tc_ptx.cuh"
+
 namespace oc {
-bool conv_tc_supported(int, int, int, int) { return false; }
-size_t conv_tc_weight_bytes(int, int, int) { return 0; }
-int prep_weights_tc(const void*, int, int, int, int, int, int, void*, cudaStream_t) { return OC_EINVAL; }
-int launch_conv_tc(const ConvArgs&, const void*, int*, cudaStream_t) { return OC_EINVAL; }
+
+__device__ int g_tc_status = 0;  // sticky: non-zero after any abandoned wait
+
+namespace tc {
+
+constexpr int TILE_M = 128;
+constexpr int KBLK = 64;                 // channels per K block = one 128-byte swizzle row
+constexpr int A_BYTES = TILE_M * 128;    // 16 KB
+constexpr int THREADS = 288;
+constexpr int LOOKAHEAD = 3;             // stages a producer keeps in flight before arriving
+constexpr int MAX_STAGES = 8;
+constexpr int MAX_NT = 256;
+
+struct Params {
+  const void* data;
+  const void* wimg;    // [n_tiles_n][K][KB][NT x 128 B] swizzled weight image
+  const void* bias;
+  const void* table;
+  void* out;
+  int64_t n_out;
+  int table_cols;
+  int K, Cin, Cout;
+  int KB;              // K blocks per tap
+  int NT;              // output channels per CTA tile (multiple of 16, <= 256)
+  int stages;
+  int tmem_cols;       // power of two >= 2 * NT
+  TapList taps;
+};
+
+struct SmemLayout {
+  uint32_t stage_bytes, ring, sidx, bias, bars, hdr, misc, total;
+};
+
+__host__ __device__ inline SmemLayout smem_layout(int NT, int stages) {
+  SmemLayout L;
+  L.stage_bytes = A_BYTES + NT * 128;
+  L.ring = 0;
+  L.sidx = L.ring + stages * L.stage_bytes;
+  L.bias = L.sidx + 2 * OC_MAX_TAPS * TILE_M * 4;
+  L.bars = L.bias + MAX_NT * 4;
+  L.hdr = L.bars + (2 * MAX_STAGES + 5) * 8;
+  L.misc = L.hdr + MAX_STAGES * 4;
+  L.total = L.misc + 64;
+  return L;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b, float ba, float bb, bool has_bias) {
+  if (BF16) {
+    __nv_bfloat16 x = __float2bfloat16_rn(a), y = __float2bfloat16_rn(b);
+    if (has_bias) {
+      x = __float2bfloat16_rn(__bfloat162float(x) + ba);
+      y = __float2bfloat16_rn(__bfloat162float(y) + bb);
+    }
+    return (uint32_t)__bfloat16_as_ushort(x) | ((uint32_t)__bfloat16_as_ushort(y) << 16);
+  } else {
+    __half x = __float2half_rn(a), y = __float2half_rn(b);
+    if (has_bias) {
+      x = __float2half_rn(__half2float(x) + ba);
+      y = __float2half_rn(__half2float(y) + bb);
+    }
+    return (uint32_t)__half_as_ushort(x) | ((uint32_t)__half_as_ushort(y) << 16);
+  }
+}
+
+template <bool BF16, typename I>
+__global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: swizzle atoms are 8 rows x 128 B
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const SmemLayout L = smem_layout(p.NT, p.stages);
+  const uint32_t s_base = smem_u32(smem);
+  int* sidx = (int*)(smem + L.sidx);
+  float* sbias = (float*)(smem + L.bias);
+  const uint32_t bars = s_base + L.bars;
+  volatile uint32_t* hdr = (volatile uint32_t*)(smem + L.hdr);
+  uint32_t* misc = (uint32_t*)(smem + L.misc);   // [0] tmem base, [1] abort flag, [2..5] warp masks
+  volatile int* abort_flag = (volatile int*)(misc + 1);
+
+  const int S = p.stages;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * MAX_STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * MAX_STAGES + 2 + a); };
+  const uint32_t psync_bar = bars + 8u * (2 * MAX_STAGES + 4);   // producers-only rendezvous
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.y * p.NT;                       // first output channel of this CTA
+  const int64_t n_tiles = (p.n_out + TILE_M - 1) / TILE_M;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_bar(s), 129);   // 128 producer arrivals + 1 arrive.expect_tx for the weights
+      mbar_init(empty_bar(s), 1);    // one tcgen05.commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 128);
+    }
+    mbar_init(psync_bar, 128);
+    misc[1] = 0;
+    fence_mbar_init();
+  }
+  for (int i = threadIdx.x; i < p.NT; i += THREADS) {
+    float b = 0.f;
+    if (p.bias && n0 + i < p.Cout)
+      b = BF16 ? __bfloat162float(((const __nv_bfloat16*)p.bias)[n0 + i]) : __half2float(((const __half*)p.bias)[n0 + i]);
+    sbias[i] = b;
+  }
+  if (warp == 0) {
+    tmem_alloc(s_base + L.misc, (uint32_t)p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = misc[0];
+
+  if (warp >= 4 && warp < 8) {
+    // ===================================================================== producers
+    const int pt = threadIdx.x - 128;          // 0..127: owns row `pt` for index prefetch
+    const int pw = warp - 4;
+    const I* table = (const I*)p.table;
+    const uint8_t* data = (const uint8_t*)p.data;
+    const size_t row_bytes = (size_t)p.Cin * 2;
+    const uint8_t* wimg = (const uint8_t*)p.wimg + (size_t)blockIdx.y * p.K * p.KB * (size_t)(p.NT * 128);
+    const uint32_t b_bytes = (uint32_t)p.NT * 128;
+    uint32_t it = 0;                           // global stage counter of this CTA
+    int nidx[OC_MAX_TAPS];
+    bool ok = true;
+    uint32_t psync_phase = 0;
+
+    auto fetch_indices = [&](int64_t tile) {
+      const int64_t r = tile * TILE_M + pt;
+#pragma unroll
+      for (int k = 0; k < OC_MAX_TAPS; ++k)
+        nidx[k] = (k < p.K && r < p.n_out) ? (int)table[r * p.table_cols + p.taps.t[k]] : -1;
+    };
+    auto publish_indices = [&](int buf) -> uint32_t {
+      uint32_t m = 0;
+      int* dst = sidx + buf * (OC_MAX_TAPS * TILE_M);
+#pragma unroll
+      for (int k = 0; k < OC_MAX_TAPS; ++k) {
+        dst[k * TILE_M + pt] = nidx[k];
+        m |= (nidx[k] >= 0 ? 1u : 0u) << k;
+      }
+      m = __reduce_or_sync(0xffffffffu, m);
+      if (lane == 0) misc[2 + pw + 4 * buf] = m;
+      // rendezvous of the 128 producer threads on an mbarrier, so that even this
+      // wait is bounded (a plain bar.sync would hang if one thread had given up)
+      mbar_arrive(psync_bar);
+      if (!mbar_wait(psync_bar, psync_phase, abort_flag, &g_tc_status, 5)) ok = false;
+      psync_phase ^= 1u;
+      return misc[2 + 4 * buf] | misc[3 + 4 * buf] | misc[4 + 4 * buf] | misc[5 + 4 * buf];
+    };
+    auto arrive_stage = [&](uint32_t j) {       // gathers of stage j have landed in smem
+      fence_proxy_async();
+      mbar_arrive(full_bar(j % S));
+    };
+
+    int64_t tile = blockIdx.x;
+    int buf = 0;
+    uint32_t mask = 0;
+    if (tile < n_tiles) {
+      fetch_indices(tile);
+      mask = publish_indices(buf);
+    }
+    for (; tile < n_tiles && ok; tile += gridDim.x) {
+      const int64_t next = tile + gridDim.x;
+      if (next < n_tiles) fetch_indices(next);   // loads stay in flight during this tile
+      if (mask == 0) mask = 1;                   // nothing valid: one all-zero stage keeps the flow uniform
+      const int* cur = sidx + buf * (OC_MAX_TAPS * TILE_M);
+      const uint32_t last_k = 31 - __clz(mask);
+      const uint32_t first_k = __ffs(mask) - 1;
+      for (uint32_t k = first_k; k <= last_k && ok; ++k) {
+        if (!((mask >> k) & 1u)) continue;
+        for (int kb = 0; kb < p.KB; ++kb) {
+          const int s = it % S;
+          if (!mbar_wait(empty_bar(s), ((it / S) & 1u) ^ 1u, abort_flag, &g_tc_status, 1)) { ok = false; break; }
+          const uint32_t a_dst = s_base + L.ring + s * L.stage_bytes;
+          const int kc = min(KBLK, p.Cin - kb * KBLK);          // channels in this block
+          if (pt == 0) {
+            hdr[s] = (k == first_k && kb == 0 ? 1u : 0u) | (k == last_k && kb == p.KB - 1 ? 2u : 0u) |
+                     ((uint32_t)(kc / 16) << 8);
+            mbar_arrive_expect_tx(full_bar(s), b_bytes);
+            bulk_g2s(a_dst + A_BYTES, wimg + ((size_t)k * p.KB + kb) * b_bytes, b_bytes, full_bar(s));
+          }
+          const int chunk = lane & 7;
+          if (chunk * 8 < kc) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int r = pw * 32 + j * 4 + (lane >> 3);
+              const int idx = cur[k * TILE_M + r];
+              const uint8_t* src = idx >= 0 ? data + (size_t)idx * row_bytes + (size_t)kb * 128 + chunk * 16 : data;
+              cp_async_16(a_dst + r * 128 + ((chunk ^ (r & 7)) << 4), src, idx >= 0 ? 16u : 0u);
+            }
+          }
+          cp_async_commit();
+          if (it >= LOOKAHEAD) {
+            cp_async_wait<LOOKAHEAD>();
+            arrive_stage(it - LOOKAHEAD);
+          }
+          ++it;
+        }
+      }
+      if (next < n_tiles) {
+        buf ^= 1;
+        mask = publish_indices(buf);
+      }
+    }
+    // drain: the last min(it, LOOKAHEAD) stages have not been signalled yet
+    cp_async_wait<0>();
+    if (ok) {
+      const uint32_t pending = it < LOOKAHEAD ? it : LOOKAHEAD;
+      for (uint32_t j = it - pending; j < it; ++j) arrive_stage(j);
+    }
+  } else if (warp == 8) {
+    // ===================================================================== MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(BF16 ? 1 : 0, 0, 0, TILE_M, p.NT);
+      uint32_t it = 0;
+      uint32_t acc = 0, acc_phase[2] = {0, 0};
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag, &g_tc_status, 2)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * (uint32_t)p.NT;
+        for (;;) {
+          const int s = it % S;
+          if (!mbar_wait(full_bar(s), (it / S) & 1u, abort_flag, &g_tc_status, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t h = hdr[s];
+          const uint32_t nk = h >> 8;
+          const uint32_t a_addr = s_base + L.ring + s * L.stage_bytes;
+          const uint32_t b_addr = a_addr + A_BYTES;
+          for (uint32_t ks = 0; ks < nk; ++ks) {
+            const uint64_t da = make_desc_sw128(a_addr + ks * 32, 16, 1024);
+            const uint64_t db = make_desc_sw128(b_addr + ks * 32, 16, 1024);
+            umma_f16(d_tmem, da, db, idesc, ((h & 1u) && ks == 0) ? 0u : 1u);
+          }
+          umma_commit(empty_bar(s));         // stage reusable once these MMAs have read it
+          ++it;
+          if (h & 2u) break;
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(acc));         // accumulator complete
+        acc_phase[acc] ^= 1u;
+        acc ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ===================================================================== epilogue (warps 0-3)
+    uint32_t acc = 0, acc_phase[2] = {0, 0};
+    const bool has_bias = p.bias != nullptr;
+    uint16_t* out = (uint16_t*)p.out;
+    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+      if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, &g_tc_status, 4)) break;
+      tc_fence_after();
+      const int64_t row = tile * TILE_M + warp * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + acc * (uint32_t)p.NT;
+      for (int c0 = 0; c0 < p.NT; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(taddr + c0, r);
+        tmem_ld_wait();
+        if (row < p.n_out && n0 + c0 < p.Cout) {
+          uint32_t o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            o[j] = pack2<BF16>(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), sbias[c0 + 2 * j],
+                               sbias[c0 + 2 * j + 1], has_bias);
+          uint4* dst = (uint4*)(out + row * p.Cout + n0 + c0);
+          dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+          dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(tempty_bar(acc));
+      acc_phase[acc] ^= 1u;
+      acc ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    // Something gave up: give copies and MMAs still in flight time to land before
+    // the shared memory and TMEM of this CTA are released.
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) {}
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// weight image: [nt][k][kb] blocks of NT rows x 128 B, row = output channel,
+// 16-byte chunk c of a row holds input channels kb*64 + c*8 .. +7 and is stored
+// at chunk position c ^ (row & 7) (the 128-byte swizzle the MMA descriptor names).
+// ---------------------------------------------------------------------------
+template <typename W, bool BF16>
+__global__ void prep_weights_tc_kernel(const W* __restrict__ w, int K, int Cin, int Cout, int transposed,
+                                       int KB, int NT, int n_tiles_n, uint16_t* __restrict__ img) {
+  const int64_t total = (int64_t)n_tiles_n * K * KB * NT * 64;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total;
+       t += (int64_t)gridDim.x * blockDim.x) {
+    const int e = (int)(t % 64);
+    const int row = (int)((t / 64) % NT);
+    const int64_t blk = t / (64 * (int64_t)NT);
+    const int kb = (int)(blk % KB);
+    const int k = (int)((blk / KB) % K);
+    const int nt = (int)(blk / ((int64_t)KB * K));
+    const int chunk = e >> 3, within = e & 7;
+    const int ci = kb * 64 + chunk * 8 + within;
+    const int co = nt * NT + row;
+    float v = 0.f;
+    if (ci < Cin && co < Cout) {
+      const int64_t src = transposed ? ((int64_t)k * Cout + co) * Cin + ci : ((int64_t)k * Cin + ci) * Cout + co;
+      v = to_f32<W>(w[src]);
+    }
+    const int64_t dst = blk * ((int64_t)NT * 64) + (int64_t)row * 64 + ((chunk ^ (row & 7)) << 3) + within;
+    img[dst] = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+  }
+}
+
+struct Plan {
+  int KB, NT, n_tiles_n, stages, tmem_cols;
+  uint32_t smem_bytes;
+  bool ok;
+};
+
+static Plan make_plan(int K, int Cin, int Cout, int dtype) {
+  Plan P = {};
+  P.ok = false;
+  if (!(dtype == OC_F16 || dtype == OC_BF16)) return P;
+  if (Cin < 16 || Cin % 16 != 0 || Cout < 16 || Cout % 16 != 0) return P;
+  if (K < 1 || K > OC_MAX_TAPS) return P;
+  P.KB = (Cin + KBLK - 1) / KBLK;
+  P.n_tiles_n = (Cout + MAX_NT - 1) / MAX_NT;
+  P.NT = ((Cout + P.n_tiles_n - 1) / P.n_tiles_n + 15) / 16 * 16;
+  P.tmem_cols = 32;
+  while (P.tmem_cols < 2 * P.NT) P.tmem_cols *= 2;
+  const uint32_t budget = 227 * 1024 - 1024;
+  int stages = MAX_STAGES;
+  while (stages > LOOKAHEAD && smem_layout(P.NT, stages).total > budget) --stages;
+  if (stages <= LOOKAHEAD) return P;
+  P.stages = stages;
+  P.smem_bytes = smem_layout(P.NT, stages).total + 1024;
+  P.ok = true;
+  return P;
+}
+
+}  // namespace tc
+
+bool conv_tc_supported(int K, int Cin, int Cout, int dtype) { return tc::make_plan(K, Cin, Cout, dtype).ok; }
+
+size_t conv_tc_weight_bytes(int K, int Cin, int Cout) {
+  const tc::Plan P = tc::make_plan(K, Cin, Cout, OC_F16);
+  return (size_t)P.n_tiles_n * K * P.KB * P.NT * 128;
+}
+
+int prep_weights_tc(const void* w, int w_dtype, int K, int Cin, int Cout, int transposed, int dtype,
+                    void* out, cudaStream_t s) {
+  const tc::Plan P = tc::make_plan(K, Cin, Cout, dtype);
+  OC_REQUIRE(P.ok, OC_EINVAL, "conv_tc: unsupported shape");
+  const int64_t total = (int64_t)P.n_tiles_n * K * P.KB * P.NT * 64;
+  const unsigned g = grid_1d(total, 256, 8);
+  uint16_t* img = (uint16_t*)out;
+  const bool bf = dtype == OC_BF16;
+  if (w_dtype == OC_F32) {
+    if (bf) tc::prep_weights_tc_kernel<float, true><<<g, 256, 0, s>>>((const float*)w, K, Cin, Cout, transposed, P.KB, P.NT, P.n_tiles_n, img);
+    else tc::prep_weights_tc_kernel<float, false><<<g, 256, 0, s>>>((const float*)w, K, Cin, Cout, transposed, P.KB, P.NT, P.n_tiles_n, img);
+  } else if (bf) {
+    tc::prep_weights_tc_kernel<__nv_bfloat16, true><<<g, 256, 0, s>>>((const __nv_bfloat16*)w, K, Cin, Cout, transposed, P.KB, P.NT, P.n_tiles_n, img);
+  } else {
+    tc::prep_weights_tc_kernel<__half, false><<<g, 256, 0, s>>>((const __half*)w, K, Cin, Cout, transposed, P.KB, P.NT, P.n_tiles_n, img);
+  }
+  OC_LAUNCH_OK("prep_weights_tc_kernel");
+  return OC_OK;
+}
+
+template <bool BF16, typename I>
+static int launch_conv_tc_t(const tc::Params& prm, const tc::Plan& P, cudaStream_t s) {
+  auto kern = tc::conv_tc_kernel<BF16, I>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  OC_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    OC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured_dev = dev;
+  }
+  const int64_t n_tiles = cdiv(prm.n_out, tc::TILE_M);
+  const int sms = sm_count();
+  dim3 grid((unsigned)(n_tiles < sms ? n_tiles : sms), (unsigned)P.n_tiles_n);
+  kern<<<grid, tc::THREADS, P.smem_bytes, s>>>(prm);
+  OC_LAUNCH_OK("conv_tc_kernel");
+  return OC_OK;
+}
+
+int launch_conv_tc(const ConvArgs& a, const void* Wimg, int* status_dev, cudaStream_t s) {
+  (void)status_dev;
+  const tc::Plan P = tc::make_plan(a.K, a.Cin, a.Cout, a.dtype);
+  OC_REQUIRE(P.ok, OC_EINVAL, "conv_tc: unsupported shape");
+  OC_REQUIRE(((uintptr_t)a.data % 16) == 0 && ((uintptr_t)a.out % 16) == 0 && ((uintptr_t)Wimg % 16) == 0,
+             OC_EINVAL, "conv_tc: data, out and workspace must be 16-byte aligned");
+  if (a.n_out == 0) return OC_OK;
+  tc::Params prm;
+  prm.data = a.data; prm.wimg = Wimg; prm.bias = a.bias; prm.table = a.table; prm.out = a.out;
+  prm.n_out = a.n_out; prm.table_cols = a.table_cols; prm.K = a.K; prm.Cin = a.Cin; prm.Cout = a.Cout;
+  prm.KB = P.KB; prm.NT = P.NT; prm.stages = P.stages; prm.tmem_cols = P.tmem_cols; prm.taps = a.taps;
+  const bool bf = a.dtype == OC_BF16;
+  if (a.idx_bytes == 8) return bf ? launch_conv_tc_t<true, int64_t>(prm, P, s) : launch_conv_tc_t<false, int64_t>(prm, P, s);
+  return bf ? launch_conv_tc_t<true, int32_t>(prm, P, s) : launch_conv_tc_t<false, int32_t>(prm, P, s);
+}
+
+// The weight gradient still runs on the FMA path; a tcgen05 version replaces these.
 bool wgrad_tc_supported(int, int, int, int) { return false; }
 size_t wgrad_tc_workspace_bytes(int, int, int, int64_t) { return 0; }
 int launch_wgrad_tc(const WgradArgs&, float*, void*, size_t, cudaStream_t) { return OC_EINVAL; }
+
+int read_tc_status(cudaStream_t s, int* h_status) {
+  int v = 0, zero = 0;
+  OC_CUDA_OK(cudaMemcpyFromSymbolAsync(&v, g_tc_status, sizeof(int), 0, cudaMemcpyDeviceToHost, s));
+  OC_CUDA_OK(cudaStreamSynchronize(s));
+  if (v != 0) OC_CUDA_OK(cudaMemcpyToSymbolAsync(g_tc_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, s));
+  *h_status = v;
+  return OC_OK;
 }
+
+}  // namespace oc

@@ -155,7 +155,7 @@ static inline unsigned grid1d(int64_t n, int threads = 256) {
 using namespace oc;
 
 extern "C" int oc_neigh_full(int depth, int batch_size, int64_t* neigh, void* stream) {
-  OC_REQUIRE(depth >= 1 && depth <= 9 && batch_size >= 1, OC_EINVAL, "oc_neigh_full: bad depth/batch");
+  OC_REQUIRE(depth >= 0 && depth <= 9 && batch_size >= 1, OC_EINVAL, "oc_neigh_full: bad depth/batch");
   const int64_t n_local = 1LL << (3 * depth);
   const int64_t total = n_local * batch_size;
   OC_REQUIRE(total < (1LL << 31), OC_EINVAL, "oc_neigh_full: layer too large");

@@ -36,7 +36,7 @@ def test_argument_errors_need_no_gpu():
   assert lib.oc_xyz2key(None, None, None, None, _lib.OC_I64, 10, 99, None, None) == -1
   assert b'depth' in lib.oc_last_error()
   assert lib.oc_xyz2key(None, None, None, None, _lib.OC_I64, 10, 5, None, None) == -1
-  assert lib.oc_neigh_full(0, 1, None, None) == -1
+  assert lib.oc_neigh_full(-1, 1, None, None) == -1
   taps = _lib.int_array([0, 1, 99])
   assert lib.oc_conv_fwd(None, 0, None, 0, 0, None, None, 8, 27, taps, 3, 10, 4, 4, 0, None, None, 0, None) == -1
   assert b'tap' in lib.oc_last_error()
