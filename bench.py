@@ -30,8 +30,9 @@ DEPTH, FULL_DEPTH, BATCH, NPTS, CH = 8, 3, 16, 100000, 64
 CONFIG_ID = 2
 
 
-def workload_clouds(rank=0, batch=BATCH, npts=NPTS):
+def workload_clouds(rank=0, batch=None, npts=NPTS):
   import ocnn_pytorch_b200 as b200
+  batch = BATCH if batch is None else batch
   clouds = [b200.synthetic.mixed_cloud(1000 * CONFIG_ID + 100 * rank + i, npts) for i in range(batch)]
   pts = np.concatenate([c[0] for c in clouds])
   nrm = np.concatenate([c[1] for c in clouds])
@@ -192,6 +193,8 @@ def run_ours(args):
 
   octree = build_octree()
   torch.cuda.synchronize()
+  if args.mode == 'conv':
+    return run_conv_only(args, b200, octree, dev)
   # octree build throughput (secondary figure): host points -> octree + all neighbour tables
   t_build = []
   for i in range(3):
@@ -322,19 +325,48 @@ def run_ours(args):
         'value': 3 * 2.0 * cnnz * CH * CH / dt / 1e12, 'unit': UNIT, 'cores': os.cpu_count() or 1,
         'kind': 'port', 'sample': '1 of %d octrees (%d rows), fp32 numpy gather-GEMM fwd+dgrad+wgrad, %.1f s' % (
             BATCH, cn, dt)}
+  b200._lib.status_check(dev)
   if rank == 0:
     print(json.dumps(line))
   if world > 1:
     dist.destroy_process_group()
 
 
+def run_conv_only(args, b200, octree, dev):
+  """Profiler mode: warm-up + `steps` conv forward/backward passes, one JSON line with the time."""
+  import torch
+  n = int(octree.nnum[DEPTH])
+  g = torch.Generator(device=dev).manual_seed(0)
+  conv = b200.nn.OctreeConv(CH, CH, [3], 1, False).to(dev).half()
+  x = torch.randn(n, CH, device=dev, generator=g).half().requires_grad_()
+  gy = torch.randn(n, CH, device=dev, generator=g).half()
+  for _ in range(args.warmup):
+    conv(x, octree, DEPTH).backward(gy)
+  torch.cuda.synchronize()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for _ in range(args.steps):
+    conv(x, octree, DEPTH).backward(gy)
+  e1.record()
+  torch.cuda.synchronize()
+  b200._lib.status_check(dev)
+  print(json.dumps({'mode': 'conv', 'rows': n, 'batch': BATCH, 'ms_per_step': e0.elapsed_time(e1) / args.steps}))
+
+
 def main():
+  global BATCH
   ap = argparse.ArgumentParser()
   ap.add_argument('--gpus', type=int, default=1)
   ap.add_argument('--steps', type=int, default=20)
   ap.add_argument('--warmup', type=int, default=5)
   ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+  ap.add_argument('--batch', type=int, default=BATCH,
+                  help='octrees per rank (default 16 = the benchmark configuration; smaller values '
+                       'are for profiler captures)')
+  ap.add_argument('--mode', default='full', choices=['full', 'conv'],
+                  help="'conv' runs only the timed conv steps (no build timing, e2e or CPU baseline)")
   args = ap.parse_args()
+  BATCH = args.batch
   if args.impl == 'reference':
     run_reference(args)
   else:
