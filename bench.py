@@ -350,7 +350,26 @@ def run_conv_only(args, b200, octree, dev):
   e1.record()
   torch.cuda.synchronize()
   b200._lib.status_check(dev)
-  print(json.dumps({'mode': 'conv', 'rows': n, 'batch': BATCH, 'ms_per_step': e0.elapsed_time(e1) / args.steps}))
+  # the three launches of a step, timed one by one
+  table, taps = octree.conv_table(DEPTH, '333', 1, False)
+  table_t, taps_t = octree.conv_table_transposed(DEPTH, '333', 1, False)
+  xd = x.detach()
+  parts = {}
+  for name, fn in (('fwd', lambda: b200.nn.conv_gather(xd, conv.weights, False, None, table, taps, CH, CH)),
+                   ('dgrad', lambda: b200.nn.conv_gather(gy, conv.weights, True, None, table_t, taps_t, CH, CH)),
+                   ('wgrad', lambda: b200.nn.conv_wgrad(xd, gy, table, taps, CH, CH))):
+    fn()
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(args.steps):
+      fn()
+    k1.record()
+    torch.cuda.synchronize()
+    parts['ms_' + name] = k0.elapsed_time(k1) / args.steps
+  out = {'mode': 'conv', 'rows': n, 'batch': BATCH, 'ms_per_step': e0.elapsed_time(e1) / args.steps}
+  out.update(parts)
+  print(json.dumps(out))
 
 
 def main():

@@ -9,13 +9,19 @@
 //
 // One persistent CTA per SM walks 128-row output tiles.  Warp roles:
 //   warps 0-3  epilogue : TMEM -> registers -> (+bias, cast) -> global
-//   warps 4-7  producers: stage = (tap, 64-channel block).  A operand: the 128
-//                         gathered input rows, copied by cp.async (16 B per lane,
-//                         8 lanes per row, zero-fill for missing neighbours) into
-//                         the 128-byte-swizzled K-major layout the MMA reads.
-//                         B operand: the matching block of the pre-swizzled weight
-//                         image, one bulk copy.  Taps with no valid neighbour in
-//                         the whole tile are skipped (warp-OR of the index signs).
+//   warps 4-7  producers: prefetch the tile's neighbour indices (one row per
+//                         thread) and publish them in shared memory.  Warp 4 then
+//                         issues the stages; stage = (tap, 64-channel block).
+//                         A operand: the 128 gathered input rows, fetched by TMA
+//                         tile::gather4 (one instruction per lane = 4 rows of 128
+//                         bytes, 32 lanes = the whole tile) straight into the
+//                         128-byte-swizzled K-major layout the MMA reads; missing
+//                         neighbours (index -1) are out of bounds and arrive as
+//                         zeros.  B operand: the matching block of the pre-swizzled
+//                         weight image, one bulk copy.  Both complete on the stage's
+//                         mbarrier by byte count, so no thread waits for its copies.
+//                         Taps with no valid neighbour in the whole tile are skipped
+//                         (warp-OR of the index signs).
 //   warp 8     MMA issuer: tcgen05.mma 128 x Cout x 16 per K step, accumulators
 //                         double-buffered in TMEM so the epilogue of tile i
 //                         overlaps the main loop of tile i+1.
@@ -24,6 +30,7 @@
 #include "oc_common.cuh"
 #include "conv_internal.cuh"
 #include "tc_ptx.cuh"
+#include <cuda.h>
 
 namespace oc {
 
@@ -35,7 +42,6 @@ constexpr int TILE_M = 128;
 constexpr int KBLK = 64;                 // channels per K block = one 128-byte swizzle row
 constexpr int A_BYTES = TILE_M * 128;    // 16 KB
 constexpr int THREADS = 288;
-constexpr int LOOKAHEAD = 3;             // stages a producer keeps in flight before arriving
 constexpr int MAX_STAGES = 8;
 constexpr int MAX_NT = 256;
 
@@ -92,7 +98,8 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, float ba, float bb, 
 }
 
 template <bool BF16, typename I>
-__global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const Params p) {
+__global__ void __launch_bounds__(THREADS, 1)
+conv_tc_kernel(const Params p, const __grid_constant__ CUtensorMap tmap) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: swizzle atoms are 8 rows x 128 B
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -118,7 +125,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const Params p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(full_bar(s), 129);   // 128 producer arrivals + 1 arrive.expect_tx for the weights
+      mbar_init(full_bar(s), 1);     // one arrive.expect_tx; the copies complete it by byte count
       mbar_init(empty_bar(s), 1);    // one tcgen05.commit
     }
     for (int a = 0; a < 2; ++a) {
@@ -149,11 +156,10 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const Params p) {
     const int pt = threadIdx.x - 128;          // 0..127: owns row `pt` for index prefetch
     const int pw = warp - 4;
     const I* table = (const I*)p.table;
-    const uint8_t* data = (const uint8_t*)p.data;
-    const size_t row_bytes = (size_t)p.Cin * 2;
     const uint8_t* wimg = (const uint8_t*)p.wimg + (size_t)blockIdx.y * p.K * p.KB * (size_t)(p.NT * 128);
     const uint32_t b_bytes = (uint32_t)p.NT * 128;
-    uint32_t it = 0;                           // global stage counter of this CTA
+    int s = 0;                                 // ring slot of the next stage
+    uint32_t ring_phase = 0;                   // flips each time the ring wraps
     int nidx[OC_MAX_TAPS];
     bool ok = true;
     uint32_t psync_phase = 0;
@@ -181,11 +187,6 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const Params p) {
       psync_phase ^= 1u;
       return misc[2 + 4 * buf] | misc[3 + 4 * buf] | misc[4 + 4 * buf] | misc[5 + 4 * buf];
     };
-    auto arrive_stage = [&](uint32_t j) {       // gathers of stage j have landed in smem
-      fence_proxy_async();
-      mbar_arrive(full_bar(j % S));
-    };
-
     int64_t tile = blockIdx.x;
     int buf = 0;
     uint32_t mask = 0;
@@ -200,35 +201,23 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const Params p) {
       const int* cur = sidx + buf * (OC_MAX_TAPS * TILE_M);
       const uint32_t last_k = 31 - __clz(mask);
       const uint32_t first_k = __ffs(mask) - 1;
-      for (uint32_t k = first_k; k <= last_k && ok; ++k) {
+      for (uint32_t k = first_k; k <= last_k && ok && pw == 0; ++k) {
         if (!((mask >> k) & 1u)) continue;
         for (int kb = 0; kb < p.KB; ++kb) {
-          const int s = it % S;
-          if (!mbar_wait(empty_bar(s), ((it / S) & 1u) ^ 1u, abort_flag, &g_tc_status, 1)) { ok = false; break; }
+          if (!mbar_wait(empty_bar(s), ring_phase ^ 1u, abort_flag, &g_tc_status, 1)) { ok = false; break; }
           const uint32_t a_dst = s_base + L.ring + s * L.stage_bytes;
           const int kc = min(KBLK, p.Cin - kb * KBLK);          // channels in this block
-          if (pt == 0) {
+          if (lane == 0) {
             hdr[s] = (k == first_k && kb == 0 ? 1u : 0u) | (k == last_k && kb == p.KB - 1 ? 2u : 0u) |
                      ((uint32_t)(kc / 16) << 8);
-            mbar_arrive_expect_tx(full_bar(s), b_bytes);
+            mbar_arrive_expect_tx(full_bar(s), (uint32_t)A_BYTES + b_bytes);
             bulk_g2s(a_dst + A_BYTES, wimg + ((size_t)k * p.KB + kb) * b_bytes, b_bytes, full_bar(s));
           }
-          const int chunk = lane & 7;
-          if (chunk * 8 < kc) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int r = pw * 32 + j * 4 + (lane >> 3);
-              const int idx = cur[k * TILE_M + r];
-              const uint8_t* src = idx >= 0 ? data + (size_t)idx * row_bytes + (size_t)kb * 128 + chunk * 16 : data;
-              cp_async_16(a_dst + r * 128 + ((chunk ^ (r & 7)) << 4), src, idx >= 0 ? 16u : 0u);
-            }
-          }
-          cp_async_commit();
-          if (it >= LOOKAHEAD) {
-            cp_async_wait<LOOKAHEAD>();
-            arrive_stage(it - LOOKAHEAD);
-          }
-          ++it;
+          __syncwarp();
+          // lane l fetches rows 4l .. 4l+3 of the tile (512 bytes of the A block)
+          const int4 r4 = *reinterpret_cast<const int4*>(cur + k * TILE_M + 4 * lane);
+          tma_gather4(a_dst + lane * 512, &tmap, kb * KBLK, r4.x, r4.y, r4.z, r4.w, full_bar(s));
+          if (++s == S) { s = 0; ring_phase ^= 1u; }
         }
       }
       if (next < n_tiles) {
@@ -236,17 +225,12 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const Params p) {
         mask = publish_indices(buf);
       }
     }
-    // drain: the last min(it, LOOKAHEAD) stages have not been signalled yet
-    cp_async_wait<0>();
-    if (ok) {
-      const uint32_t pending = it < LOOKAHEAD ? it : LOOKAHEAD;
-      for (uint32_t j = it - pending; j < it; ++j) arrive_stage(j);
-    }
   } else if (warp == 8) {
     // ===================================================================== MMA issuer
     if (lane == 0) {
       const uint32_t idesc = make_idesc(BF16 ? 1 : 0, 0, 0, TILE_M, p.NT);
-      uint32_t it = 0;
+      int s = 0;
+      uint32_t ring_phase = 0;
       uint32_t acc = 0, acc_phase[2] = {0, 0};
       bool ok = true;
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
@@ -254,8 +238,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const Params p) {
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * (uint32_t)p.NT;
         for (;;) {
-          const int s = it % S;
-          if (!mbar_wait(full_bar(s), (it / S) & 1u, abort_flag, &g_tc_status, 3)) { ok = false; break; }
+          if (!mbar_wait(full_bar(s), ring_phase, abort_flag, &g_tc_status, 3)) { ok = false; break; }
           tc_fence_after();
           const uint32_t h = hdr[s];
           const uint32_t nk = h >> 8;
@@ -267,7 +250,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const Params p) {
             umma_f16(d_tmem, da, db, idesc, ((h & 1u) && ks == 0) ? 0u : 1u);
           }
           umma_commit(empty_bar(s));         // stage reusable once these MMAs have read it
-          ++it;
+          if (++s == S) { s = 0; ring_phase ^= 1u; }
           if (h & 2u) break;
         }
         if (!ok) break;
@@ -283,7 +266,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tc_kernel(const Params p) {
     const bool has_bias = p.bias != nullptr;
     uint16_t* out = (uint16_t*)p.out;
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-      if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, &g_tc_status, 4)) break;
+      if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, &g_tc_status, 4, 256)) break;
       tc_fence_after();
       const int64_t row = tile * TILE_M + warp * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + acc * (uint32_t)p.NT;
@@ -373,8 +356,8 @@ static Plan make_plan(int K, int Cin, int Cout, int dtype) {
   while (P.tmem_cols < 2 * P.NT) P.tmem_cols *= 2;
   const uint32_t budget = 227 * 1024 - 1024;
   int stages = MAX_STAGES;
-  while (stages > LOOKAHEAD && smem_layout(P.NT, stages).total > budget) --stages;
-  if (stages <= LOOKAHEAD) return P;
+  while (stages > 2 && smem_layout(P.NT, stages).total > budget) --stages;
+  if (smem_layout(P.NT, stages).total > budget) return P;
   P.stages = stages;
   P.smem_bytes = smem_layout(P.NT, stages).total + 1024;
   P.ok = true;
@@ -410,8 +393,47 @@ int prep_weights_tc(const void* w, int w_dtype, int K, int Cin, int Cout, int tr
   return OC_OK;
 }
 
+// cuTensorMapEncodeTiled is a driver entry point; it is resolved through the
+// runtime so that the library links against cudart only.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static int get_encode_fn(EncodeTiledFn* out) {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    OC_CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q));
+    OC_REQUIRE(ptr && q == cudaDriverEntryPointSuccess, OC_ECUDA, "cuTensorMapEncodeTiled is not available");
+    fn = (EncodeTiledFn)ptr;
+  }
+  *out = fn;
+  return OC_OK;
+}
+
+// 2-D map of a row-major (rows, channels) 16-bit matrix for tile::gather4 loads:
+// box = 64 channels x 1 row (the instruction names 4 rows), 128-byte swizzle,
+// out-of-bounds elements (row index -1, channels past the end) read as zero.
+int make_gather_tensor_map(const void* data, int64_t rows, int channels, CUtensorMap* tmap) {
+  EncodeTiledFn encode;
+  int rc = get_encode_fn(&encode);
+  if (rc) return rc;
+  const cuuint64_t gdim[2] = {(cuuint64_t)channels, (cuuint64_t)(rows > 0 ? rows : 1)};
+  const cuuint64_t gstride[1] = {(cuuint64_t)channels * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)tc::KBLK, 1};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(tmap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(data), gdim, gstride, box,
+                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  OC_REQUIRE(r == CUDA_SUCCESS, OC_ECUDA, "cuTensorMapEncodeTiled failed with code %d (rows %lld, channels %d)",
+             (int)r, (long long)rows, channels);
+  return OC_OK;
+}
+
 template <bool BF16, typename I>
-static int launch_conv_tc_t(const tc::Params& prm, const tc::Plan& P, cudaStream_t s) {
+static int launch_conv_tc_t(const tc::Params& prm, const tc::Plan& P, const CUtensorMap& tmap, cudaStream_t s) {
   auto kern = tc::conv_tc_kernel<BF16, I>;
   static thread_local int configured_dev = -1;
   int dev = 0;
@@ -423,7 +445,7 @@ static int launch_conv_tc_t(const tc::Params& prm, const tc::Plan& P, cudaStream
   const int64_t n_tiles = cdiv(prm.n_out, tc::TILE_M);
   const int sms = sm_count();
   dim3 grid((unsigned)(n_tiles < sms ? n_tiles : sms), (unsigned)P.n_tiles_n);
-  kern<<<grid, tc::THREADS, P.smem_bytes, s>>>(prm);
+  kern<<<grid, tc::THREADS, P.smem_bytes, s>>>(prm, tmap);
   OC_LAUNCH_OK("conv_tc_kernel");
   return OC_OK;
 }
@@ -439,9 +461,13 @@ int launch_conv_tc(const ConvArgs& a, const void* Wimg, int* status_dev, cudaStr
   prm.data = a.data; prm.wimg = Wimg; prm.bias = a.bias; prm.table = a.table; prm.out = a.out;
   prm.n_out = a.n_out; prm.table_cols = a.table_cols; prm.K = a.K; prm.Cin = a.Cin; prm.Cout = a.Cout;
   prm.KB = P.KB; prm.NT = P.NT; prm.stages = P.stages; prm.tmem_cols = P.tmem_cols; prm.taps = a.taps;
+  CUtensorMap tmap;
+  int rc = make_gather_tensor_map(a.data, a.n_in, a.Cin, &tmap);
+  if (rc) return rc;
   const bool bf = a.dtype == OC_BF16;
-  if (a.idx_bytes == 8) return bf ? launch_conv_tc_t<true, int64_t>(prm, P, s) : launch_conv_tc_t<false, int64_t>(prm, P, s);
-  return bf ? launch_conv_tc_t<true, int32_t>(prm, P, s) : launch_conv_tc_t<false, int32_t>(prm, P, s);
+  if (a.idx_bytes == 8)
+    return bf ? launch_conv_tc_t<true, int64_t>(prm, P, tmap, s) : launch_conv_tc_t<false, int64_t>(prm, P, tmap, s);
+  return bf ? launch_conv_tc_t<true, int32_t>(prm, P, tmap, s) : launch_conv_tc_t<false, int32_t>(prm, P, tmap, s);
 }
 
 // The weight gradient still runs on the FMA path; a tcgen05 version replaces these.

@@ -32,26 +32,58 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
                "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// One poll.  The suspend-time hint lets the hardware park the thread until the
+// phase completes or `hint_ns` elapse, instead of burning issue slots.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+// Non-blocking poll (never parks the thread).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
 }
-// Returns false if the wait was abandoned (own limit reached or another role
-// already aborted).  `abort_flag` lives in shared memory.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+// Busy-polling variant for the short, latency-critical waits of the main loop.
+__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status_word, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_test_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t i = 0; i < 0xffffffffu; ++i) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > WAIT_CYCLES) break;
+    }
+  }
+  *abort_flag = 1;
+  atomicMax(status_word, code);
+  return false;
+}
+// Returns false if the wait was abandoned (own limit reached or another role
+// already aborted).  `abort_flag` lives in shared memory.  `backoff_ns` > 0 adds a
+// sleep between polls for roles whose waits are long (epilogue).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status_word, int code, uint32_t backoff_ns = 0) {
+  if (mbar_try_wait(bar, parity, 2000u)) return true;
   const long long t0 = clock64();
   for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u) {
+    if (backoff_ns) __nanosleep(backoff_ns);
+    if (mbar_try_wait(bar, parity, 20000u)) return true;
+    if ((i & 15u) == 15u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > WAIT_CYCLES) break;
     }
@@ -70,6 +102,22 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
+// wait until at most n (0..4) commit groups of this thread are pending
+__device__ __forceinline__ void cp_async_wait_dyn(int n) {
+  switch (n) {
+    case 0: cp_async_wait<0>(); break;
+    case 1: cp_async_wait<1>(); break;
+    case 2: cp_async_wait<2>(); break;
+    case 3: cp_async_wait<3>(); break;
+    default: cp_async_wait<4>(); break;
+  }
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// mbarrier arrival triggered by the completion of all prior cp.async of this thread;
+// .noinc: it counts as one of the arrivals the barrier was initialised to expect.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 // generic-proxy writes (cp.async, st.shared) -> visible to the async proxy (tcgen05.mma)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -78,6 +126,18 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
+}
+
+// ---- TMA tile::gather4: four rows (row indices r0..r3, first column c0) of a 2-D
+// tensor -> 4 consecutive swizzled rows of shared memory; rows outside the tensor
+// (e.g. index -1) are filled with zeros.  Completion is counted in bytes on `bar`.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tensor_map, int c0, int r0, int r1, int r2,
+                                            int r3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, "
+      "%5, %6}], [%7];" ::"r"(dst),
+      "l"(tensor_map), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar)
+      : "memory");
 }
 
 // ---- TMEM -------------------------------------------------------------------
