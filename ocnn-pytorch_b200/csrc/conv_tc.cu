@@ -9,20 +9,17 @@
 //
 // One persistent CTA per SM walks 128-row output tiles.  Warp roles:
 //   warps 0-3  epilogue : TMEM -> registers -> (+bias, cast) -> global
-//   warps 4-7  producers: prefetch the tile's neighbour indices (one row per
-//                         thread) and publish them in shared memory.  Warp 4 then
-//                         issues the stages; stage = (tap, 64-channel block).
-//                         A operand: the 128 gathered input rows, fetched by TMA
-//                         tile::gather4 (one instruction per lane = 4 rows of 128
-//                         bytes, 32 lanes = the whole tile) straight into the
-//                         128-byte-swizzled K-major layout the MMA reads; missing
-//                         neighbours (index -1) are out of bounds and arrive as
-//                         zeros.  B operand: the matching block of the pre-swizzled
-//                         weight image, one bulk copy.  Both complete on the stage's
-//                         mbarrier by byte count, so no thread waits for its copies.
-//                         Taps with no valid neighbour in the whole tile are skipped
-//                         (warp-OR of the index signs).
-//   warp 8     MMA issuer: tcgen05.mma 128 x Cout x 16 per K step, accumulators
+//   warps 4-11 producers: prefetch the tile's neighbour indices and publish them in
+//                         shared memory, then issue the stages; stage = (tap,
+//                         64-channel block).  A operand: the 128 gathered input rows,
+//                         copied by cp.async (16 B per lane, 8 lanes per row,
+//                         zero-fill for missing neighbours) into the 128-byte-
+//                         swizzled K-major layout the MMA reads; each thread's
+//                         completion arrives on the stage barrier, nobody waits.
+//                         B operand: the matching block of the pre-swizzled weight
+//                         image, one bulk copy.  Taps with no valid neighbour in
+//                         the whole tile are skipped (warp-OR of the index signs).
+//   warp 12    MMA issuer: tcgen05.mma 128 x Cout x 16 per K step, accumulators
 //                         double-buffered in TMEM so the epilogue of tile i
 //                         overlaps the main loop of tile i+1.
 // Stages flow through a ring of full/empty mbarriers; a per-stage header tells
@@ -30,7 +27,6 @@
 #include "oc_common.cuh"
 #include "conv_internal.cuh"
 #include "tc_ptx.cuh"
-#include <cuda.h>
 
 namespace oc {
 
@@ -41,7 +37,10 @@ namespace tc {
 constexpr int TILE_M = 128;
 constexpr int KBLK = 64;                 // channels per K block = one 128-byte swizzle row
 constexpr int A_BYTES = TILE_M * 128;    // 16 KB
-constexpr int THREADS = 288;
+constexpr int PROD_WARPS = 8;             // warps 4..11 gather; warp 12 issues the MMAs
+constexpr int PROD_THREADS = PROD_WARPS * 32;
+constexpr int MMA_WARP = 4 + PROD_WARPS;
+constexpr int THREADS = (MMA_WARP + 1) * 32;
 constexpr int MAX_STAGES = 8;
 constexpr int MAX_NT = 256;
 
@@ -74,7 +73,7 @@ __host__ __device__ inline SmemLayout smem_layout(int NT, int stages) {
   L.bars = L.bias + MAX_NT * 4;
   L.hdr = L.bars + (2 * MAX_STAGES + 5) * 8;
   L.misc = L.hdr + MAX_STAGES * 4;
-  L.total = L.misc + 64;
+  L.total = L.misc + 128;
   return L;
 }
 
@@ -99,7 +98,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, float ba, float bb, 
 
 template <bool BF16, typename I>
 __global__ void __launch_bounds__(THREADS, 1)
-conv_tc_kernel(const Params p, const __grid_constant__ CUtensorMap tmap) {
+conv_tc_kernel(const Params p) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: swizzle atoms are 8 rows x 128 B
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -109,7 +108,7 @@ conv_tc_kernel(const Params p, const __grid_constant__ CUtensorMap tmap) {
   float* sbias = (float*)(smem + L.bias);
   const uint32_t bars = s_base + L.bars;
   volatile uint32_t* hdr = (volatile uint32_t*)(smem + L.hdr);
-  uint32_t* misc = (uint32_t*)(smem + L.misc);   // [0] tmem base, [1] abort flag, [2..5] warp masks
+  uint32_t* misc = (uint32_t*)(smem + L.misc);   // [0] tmem base, [1] abort flag, [2..17] warp masks (2 buffers)
   volatile int* abort_flag = (volatile int*)(misc + 1);
 
   const int S = p.stages;
@@ -125,14 +124,14 @@ conv_tc_kernel(const Params p, const __grid_constant__ CUtensorMap tmap) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(full_bar(s), 1);     // one arrive.expect_tx; the copies complete it by byte count
+      mbar_init(full_bar(s), PROD_THREADS + 1);   // every producer thread's copies + 1 arrive.expect_tx (weights)
       mbar_init(empty_bar(s), 1);    // one tcgen05.commit
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), 128);
     }
-    mbar_init(psync_bar, 128);
+    mbar_init(psync_bar, PROD_THREADS);
     misc[1] = 0;
     fence_mbar_init();
   }
@@ -151,41 +150,61 @@ conv_tc_kernel(const Params p, const __grid_constant__ CUtensorMap tmap) {
   tc_fence_after();
   const uint32_t tmem_base = misc[0];
 
-  if (warp >= 4 && warp < 8) {
+  if (warp >= 4 && warp < MMA_WARP) {
     // ===================================================================== producers
-    const int pt = threadIdx.x - 128;          // 0..127: owns row `pt` for index prefetch
+    const int pt = threadIdx.x - 128;          // 0..255
     const int pw = warp - 4;
+    const int frow = pt & (TILE_M - 1);        // index prefetch: row `frow`, taps of parity `fhalf`
+    const int fhalf = pt >> 7;
     const I* table = (const I*)p.table;
+    const uint8_t* data = (const uint8_t*)p.data;
+    const uint32_t row_bytes = (uint32_t)p.Cin * 2;
     const uint8_t* wimg = (const uint8_t*)p.wimg + (size_t)blockIdx.y * p.K * p.KB * (size_t)(p.NT * 128);
     const uint32_t b_bytes = (uint32_t)p.NT * 128;
+    // gather mapping: 8 lanes copy one 128-byte row (16 B each); a lane owns 4
+    // consecutive rows of its warp's 16, so their indices come with one 16-byte load
+    const int chunk = lane & 7;
+    const int row0 = pw * 16 + (lane >> 3) * 4;
+    uint32_t doff[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) doff[j] = (uint32_t)((row0 + j) * 128 + ((chunk ^ ((row0 + j) & 7)) << 4));
     int s = 0;                                 // ring slot of the next stage
     uint32_t ring_phase = 0;                   // flips each time the ring wraps
-    int nidx[OC_MAX_TAPS];
+    constexpr int NF = (OC_MAX_TAPS + 1) / 2;
+    int nidx[NF];
     bool ok = true;
     uint32_t psync_phase = 0;
 
     auto fetch_indices = [&](int64_t tile) {
-      const int64_t r = tile * TILE_M + pt;
+      const int64_t r = tile * TILE_M + frow;
 #pragma unroll
-      for (int k = 0; k < OC_MAX_TAPS; ++k)
-        nidx[k] = (k < p.K && r < p.n_out) ? (int)table[r * p.table_cols + p.taps.t[k]] : -1;
+      for (int i = 0; i < NF; ++i) {
+        const int k = 2 * i + fhalf;
+        nidx[i] = (k < p.K && r < p.n_out) ? (int)table[r * p.table_cols + p.taps.t[k < OC_MAX_TAPS ? k : 0]] : -1;
+      }
     };
     auto publish_indices = [&](int buf) -> uint32_t {
       uint32_t m = 0;
       int* dst = sidx + buf * (OC_MAX_TAPS * TILE_M);
 #pragma unroll
-      for (int k = 0; k < OC_MAX_TAPS; ++k) {
-        dst[k * TILE_M + pt] = nidx[k];
-        m |= (nidx[k] >= 0 ? 1u : 0u) << k;
+      for (int i = 0; i < NF; ++i) {
+        const int k = 2 * i + fhalf;
+        if (k < OC_MAX_TAPS) {
+          dst[k * TILE_M + frow] = nidx[i];
+          m |= (nidx[i] >= 0 ? 1u : 0u) << k;
+        }
       }
       m = __reduce_or_sync(0xffffffffu, m);
-      if (lane == 0) misc[2 + pw + 4 * buf] = m;
-      // rendezvous of the 128 producer threads on an mbarrier, so that even this
-      // wait is bounded (a plain bar.sync would hang if one thread had given up)
+      if (lane == 0) misc[2 + pw + PROD_WARPS * buf] = m;
+      // rendezvous of the producer threads on an mbarrier, so that even this wait
+      // is bounded (a plain bar.sync would hang if one thread had given up)
       mbar_arrive(psync_bar);
       if (!mbar_wait(psync_bar, psync_phase, abort_flag, &g_tc_status, 5)) ok = false;
       psync_phase ^= 1u;
-      return misc[2 + 4 * buf] | misc[3 + 4 * buf] | misc[4 + 4 * buf] | misc[5 + 4 * buf];
+      uint32_t all = 0;
+#pragma unroll
+      for (int w = 0; w < PROD_WARPS; ++w) all |= misc[2 + w + PROD_WARPS * buf];
+      return all;
     };
     int64_t tile = blockIdx.x;
     int buf = 0;
@@ -201,22 +220,32 @@ conv_tc_kernel(const Params p, const __grid_constant__ CUtensorMap tmap) {
       const int* cur = sidx + buf * (OC_MAX_TAPS * TILE_M);
       const uint32_t last_k = 31 - __clz(mask);
       const uint32_t first_k = __ffs(mask) - 1;
-      for (uint32_t k = first_k; k <= last_k && ok && pw == 0; ++k) {
+      for (uint32_t k = first_k; k <= last_k && ok; ++k) {
         if (!((mask >> k) & 1u)) continue;
+        // the 4 row indices of this lane for tap k: read before any copy is issued
+        const int4 r4 = *reinterpret_cast<const int4*>(cur + k * TILE_M + row0);
+        const int rid[4] = {r4.x, r4.y, r4.z, r4.w};
         for (int kb = 0; kb < p.KB; ++kb) {
           if (!mbar_wait(empty_bar(s), ring_phase ^ 1u, abort_flag, &g_tc_status, 1)) { ok = false; break; }
           const uint32_t a_dst = s_base + L.ring + s * L.stage_bytes;
           const int kc = min(KBLK, p.Cin - kb * KBLK);          // channels in this block
-          if (lane == 0) {
+          if (pt == 0) {
             hdr[s] = (k == first_k && kb == 0 ? 1u : 0u) | (k == last_k && kb == p.KB - 1 ? 2u : 0u) |
                      ((uint32_t)(kc / 16) << 8);
-            mbar_arrive_expect_tx(full_bar(s), (uint32_t)A_BYTES + b_bytes);
+            mbar_arrive_expect_tx(full_bar(s), b_bytes);
             bulk_g2s(a_dst + A_BYTES, wimg + ((size_t)k * p.KB + kb) * b_bytes, b_bytes, full_bar(s));
           }
-          __syncwarp();
-          // lane l fetches rows 4l .. 4l+3 of the tile (512 bytes of the A block)
-          const int4 r4 = *reinterpret_cast<const int4*>(cur + k * TILE_M + 4 * lane);
-          tma_gather4(a_dst + lane * 512, &tmap, kb * KBLK, r4.x, r4.y, r4.z, r4.w, full_bar(s));
+          if (chunk * 8 < kc) {
+            const uint8_t* lane_src = data + (size_t)kb * 128 + chunk * 16;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int idx = rid[j];
+              cp_async_16(a_dst + doff[j], lane_src + (size_t)(idx < 0 ? 0 : idx) * row_bytes, idx >= 0 ? 16u : 0u);
+            }
+          }
+          // arrives on the stage's barrier once this thread's copies have landed; the
+          // thread itself does not wait, so up to `stages` gathers stay in flight
+          cp_async_arrive_noinc(full_bar(s));
           if (++s == S) { s = 0; ring_phase ^= 1u; }
         }
       }
@@ -225,7 +254,8 @@ conv_tc_kernel(const Params p, const __grid_constant__ CUtensorMap tmap) {
         mask = publish_indices(buf);
       }
     }
-  } else if (warp == 8) {
+    cp_async_wait_all();   // nothing of this thread may still be writing shared memory at exit
+  } else if (warp == MMA_WARP) {
     // ===================================================================== MMA issuer
     if (lane == 0) {
       const uint32_t idesc = make_idesc(BF16 ? 1 : 0, 0, 0, TILE_M, p.NT);
@@ -393,47 +423,8 @@ int prep_weights_tc(const void* w, int w_dtype, int K, int Cin, int Cout, int tr
   return OC_OK;
 }
 
-// cuTensorMapEncodeTiled is a driver entry point; it is resolved through the
-// runtime so that the library links against cudart only.
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-static int get_encode_fn(EncodeTiledFn* out) {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    OC_CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q));
-    OC_REQUIRE(ptr && q == cudaDriverEntryPointSuccess, OC_ECUDA, "cuTensorMapEncodeTiled is not available");
-    fn = (EncodeTiledFn)ptr;
-  }
-  *out = fn;
-  return OC_OK;
-}
-
-// 2-D map of a row-major (rows, channels) 16-bit matrix for tile::gather4 loads:
-// box = 64 channels x 1 row (the instruction names 4 rows), 128-byte swizzle,
-// out-of-bounds elements (row index -1, channels past the end) read as zero.
-int make_gather_tensor_map(const void* data, int64_t rows, int channels, CUtensorMap* tmap) {
-  EncodeTiledFn encode;
-  int rc = get_encode_fn(&encode);
-  if (rc) return rc;
-  const cuuint64_t gdim[2] = {(cuuint64_t)channels, (cuuint64_t)(rows > 0 ? rows : 1)};
-  const cuuint64_t gstride[1] = {(cuuint64_t)channels * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)tc::KBLK, 1};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = encode(tmap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(data), gdim, gstride, box,
-                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  OC_REQUIRE(r == CUDA_SUCCESS, OC_ECUDA, "cuTensorMapEncodeTiled failed with code %d (rows %lld, channels %d)",
-             (int)r, (long long)rows, channels);
-  return OC_OK;
-}
-
 template <bool BF16, typename I>
-static int launch_conv_tc_t(const tc::Params& prm, const tc::Plan& P, const CUtensorMap& tmap, cudaStream_t s) {
+static int launch_conv_tc_t(const tc::Params& prm, const tc::Plan& P, cudaStream_t s) {
   auto kern = tc::conv_tc_kernel<BF16, I>;
   static thread_local int configured_dev = -1;
   int dev = 0;
@@ -445,7 +436,7 @@ static int launch_conv_tc_t(const tc::Params& prm, const tc::Plan& P, const CUte
   const int64_t n_tiles = cdiv(prm.n_out, tc::TILE_M);
   const int sms = sm_count();
   dim3 grid((unsigned)(n_tiles < sms ? n_tiles : sms), (unsigned)P.n_tiles_n);
-  kern<<<grid, tc::THREADS, P.smem_bytes, s>>>(prm, tmap);
+  kern<<<grid, tc::THREADS, P.smem_bytes, s>>>(prm);
   OC_LAUNCH_OK("conv_tc_kernel");
   return OC_OK;
 }
@@ -461,13 +452,9 @@ int launch_conv_tc(const ConvArgs& a, const void* Wimg, int* status_dev, cudaStr
   prm.data = a.data; prm.wimg = Wimg; prm.bias = a.bias; prm.table = a.table; prm.out = a.out;
   prm.n_out = a.n_out; prm.table_cols = a.table_cols; prm.K = a.K; prm.Cin = a.Cin; prm.Cout = a.Cout;
   prm.KB = P.KB; prm.NT = P.NT; prm.stages = P.stages; prm.tmem_cols = P.tmem_cols; prm.taps = a.taps;
-  CUtensorMap tmap;
-  int rc = make_gather_tensor_map(a.data, a.n_in, a.Cin, &tmap);
-  if (rc) return rc;
   const bool bf = a.dtype == OC_BF16;
-  if (a.idx_bytes == 8)
-    return bf ? launch_conv_tc_t<true, int64_t>(prm, P, tmap, s) : launch_conv_tc_t<false, int64_t>(prm, P, tmap, s);
-  return bf ? launch_conv_tc_t<true, int32_t>(prm, P, tmap, s) : launch_conv_tc_t<false, int32_t>(prm, P, tmap, s);
+  if (a.idx_bytes == 8) return bf ? launch_conv_tc_t<true, int64_t>(prm, P, s) : launch_conv_tc_t<false, int64_t>(prm, P, s);
+  return bf ? launch_conv_tc_t<true, int32_t>(prm, P, s) : launch_conv_tc_t<false, int32_t>(prm, P, s);
 }
 
 // The weight gradient still runs on the FMA path; a tcgen05 version replaces these.

@@ -128,18 +128,6 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                : "memory");
 }
 
-// ---- TMA tile::gather4: four rows (row indices r0..r3, first column c0) of a 2-D
-// tensor -> 4 consecutive swizzled rows of shared memory; rows outside the tensor
-// (e.g. index -1) are filled with zeros.  Completion is counted in bytes on `bar`.
-__device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tensor_map, int c0, int r0, int r1, int r2,
-                                            int r3, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, "
-      "%5, %6}], [%7];" ::"r"(dst),
-      "l"(tensor_map), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar)
-      : "memory");
-}
-
 // ---- TMEM -------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
