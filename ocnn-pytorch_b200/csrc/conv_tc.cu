@@ -457,11 +457,6 @@ int launch_conv_tc(const ConvArgs& a, const void* Wimg, int* status_dev, cudaStr
   return bf ? launch_conv_tc_t<true, int32_t>(prm, P, s) : launch_conv_tc_t<false, int32_t>(prm, P, s);
 }
 
-// The weight gradient still runs on the FMA path; a tcgen05 version replaces these.
-bool wgrad_tc_supported(int, int, int, int) { return false; }
-size_t wgrad_tc_workspace_bytes(int, int, int, int64_t) { return 0; }
-int launch_wgrad_tc(const WgradArgs&, float*, void*, size_t, cudaStream_t) { return OC_EINVAL; }
-
 int read_tc_status(cudaStream_t s, int* h_status) {
   int v = 0, zero = 0;
   OC_CUDA_OK(cudaMemcpyFromSymbolAsync(&v, g_tc_status, sizeof(int), 0, cudaMemcpyDeviceToHost, s));
@@ -472,3 +467,5 @@ int read_tc_status(cudaStream_t s, int* h_status) {
 }
 
 }  // namespace oc
+
+#include "wgrad_tc.cuh"

@@ -1,0 +1,474 @@
+// Weight gradient of the octree convolution on tcgen05 tensor cores (fp16 / bf16
+// data, fp32 accumulation in TMEM):
+//     grad_w[k, ci, co] = sum_r data[table[r, taps[k]], ci] * grad_out[r, co]
+// It replaces weight_gemm of ocnn/nn/octree_conv.py:170-202 and the Triton
+// kernels conv_bwd_weight_implicit_gemm(_splitk) of the reference.
+//
+// As a GEMM the reduction runs over the rows r, so both operands are "MN-major"
+// for the MMA: a gathered tile (128 rows x 64 channels, one 128-byte swizzled
+// line per row — byte for byte the A tile of the forward kernel) is read
+// transposed as a 64 x 128 block of the M x K operand, and a dense tile of
+// grad_out rows is the K x N operand.  Two 64-channel blocks (two taps, or the
+// two halves of one tap when Cin > 64) form one 128-row M tile.
+//
+// Work split: grid = (row slices, M-tile groups, N tiles).  A CTA walks the 128-row
+// tiles of its slice; per tile it loads grad_out once and, for every M tile of its
+// group with at least one valid neighbour, gathers the two blocks and issues
+// 8 MMAs (K = 16 rows each) into that M tile's own TMEM accumulator, which stays
+// resident for the whole slice.  At the end every accumulator is written to a
+// per-slice fp32 partial and a second kernel adds the slices in a fixed order
+// (no atomics: the result does not vary from run to run).
+// (Included at the end of conv_tc.cu: both kernels share the sticky status word,
+// and the library is built without relocatable device code.)
+#pragma once
+
+namespace oc {
+
+namespace wg {
+
+using namespace tc;
+
+constexpr int TILE_R = 128;               // rows (the MMA K extent) per tile
+constexpr int BLK_BYTES = TILE_R * 128;   // one 64-channel block of 128 rows
+constexpr int PROD_WARPS = 8;
+constexpr int PROD_THREADS = PROD_WARPS * 32;
+constexpr int MMA_WARP = 4 + PROD_WARPS;
+constexpr int THREADS = (MMA_WARP + 1) * 32;
+constexpr int MAX_STAGES = 6;
+constexpr int MAX_MT = 16;                // M tiles (accumulators) per CTA
+
+struct Params {
+  const void* data;
+  const void* gout;
+  const void* table;
+  float* partial;       // [row slices][K][Cin][Cout]
+  int64_t n_out;
+  int64_t tiles_per_slice;
+  int table_cols;
+  int K, Cin, Cout;
+  int KB;               // 64-channel blocks per tap
+  int nblk;             // K * KB
+  int NTW;              // output channels per CTA (multiple of 16, <= 128)
+  int GB;               // 64-column blocks of grad_out per tile = ceil(NTW / 64)
+  int mt_per_cta;
+  int stages;
+  int tmem_cols;
+  TapList taps;
+};
+
+struct SmemLayout {
+  uint32_t ring, gbuf, sidx, bars, hdr, misc, total;
+};
+
+__host__ __device__ inline SmemLayout smem_layout(int GB, int stages) {
+  SmemLayout L;
+  L.ring = 0;                                     // stages x 2 blocks
+  L.gbuf = L.ring + stages * 2 * BLK_BYTES;       // 2 buffers x GB blocks
+  L.sidx = L.gbuf + 2 * GB * BLK_BYTES;
+  L.bars = L.sidx + 2 * OC_MAX_TAPS * TILE_R * 4;
+  L.hdr = L.bars + (2 * MAX_STAGES + 6) * 8;
+  L.misc = L.hdr + MAX_STAGES * 4;
+  L.total = L.misc + 128;
+  return L;
+}
+
+template <bool BF16, typename I>
+__global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const SmemLayout L = smem_layout(p.GB, p.stages);
+  const uint32_t s_base = smem_u32(smem);
+  int* sidx = (int*)(smem + L.sidx);
+  const uint32_t bars = s_base + L.bars;
+  volatile uint32_t* hdr = (volatile uint32_t*)(smem + L.hdr);
+  uint32_t* misc = (uint32_t*)(smem + L.misc);   // [0] tmem base, [1] abort, [2..17] warp masks, [18] touched
+  volatile int* abort_flag = (volatile int*)(misc + 1);
+
+  const int S = p.stages;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
+  auto gfull_bar = [&](int g) { return bars + 8u * (2 * MAX_STAGES + g); };
+  auto gempty_bar = [&](int g) { return bars + 8u * (2 * MAX_STAGES + 2 + g); };
+  const uint32_t psync_bar = bars + 8u * (2 * MAX_STAGES + 4);
+  const uint32_t done_bar = bars + 8u * (2 * MAX_STAGES + 5);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slice = blockIdx.x;
+  const int m_lo = blockIdx.y * p.mt_per_cta;                     // first M tile of this CTA
+  const int n_mt_all = (p.nblk + 1) / 2;
+  const int m_cnt = min(p.mt_per_cta, n_mt_all - m_lo);
+  const int n0 = blockIdx.z * p.NTW;
+  const int64_t n_tiles = (p.n_out + TILE_R - 1) / TILE_R;
+  const int64_t t_begin = (int64_t)slice * p.tiles_per_slice;
+  const int64_t t_end = min(n_tiles, t_begin + p.tiles_per_slice);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_bar(s), PROD_THREADS + 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(gfull_bar(g), PROD_THREADS);
+      mbar_init(gempty_bar(g), 1);
+    }
+    mbar_init(psync_bar, PROD_THREADS);
+    mbar_init(done_bar, 1);
+    misc[1] = 0;
+    misc[18] = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(s_base + L.misc, (uint32_t)p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = misc[0];
+
+  // taps that feed this CTA's M tiles
+  uint32_t group_taps = 0;
+  for (int b = 2 * m_lo; b < 2 * (m_lo + m_cnt) && b < p.nblk; ++b) group_taps |= 1u << (b / p.KB);
+
+  if (warp >= 4 && warp < MMA_WARP) {
+    // ===================================================================== producers
+    const int pt = threadIdx.x - 128;
+    const int pw = warp - 4;
+    const int frow = pt & (TILE_R - 1);
+    const int fhalf = pt >> 7;
+    const I* table = (const I*)p.table;
+    const uint8_t* data = (const uint8_t*)p.data;
+    const uint8_t* gout = (const uint8_t*)p.gout;
+    const uint32_t row_bytes = (uint32_t)p.Cin * 2;
+    const uint32_t grow_bytes = (uint32_t)p.Cout * 2;
+    const int chunk = lane & 7;
+    const int row0 = pw * 16 + (lane >> 3) * 4;
+    uint32_t doff[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) doff[j] = (uint32_t)((row0 + j) * 128 + ((chunk ^ ((row0 + j) & 7)) << 4));
+    int s = 0;
+    uint32_t ring_phase = 0;
+    uint32_t gb_sel = 0, g_phase[2] = {0, 0};
+    constexpr int NF = (OC_MAX_TAPS + 1) / 2;
+    int nidx[NF];
+    bool ok = true;
+    uint32_t psync_phase = 0;
+    uint32_t touched = 0;
+
+    auto fetch_indices = [&](int64_t tile) {
+      const int64_t r = tile * TILE_R + frow;
+#pragma unroll
+      for (int i = 0; i < NF; ++i) {
+        const int k = 2 * i + fhalf;
+        const bool want = k < p.K && ((group_taps >> k) & 1u) && r < p.n_out;
+        nidx[i] = want ? (int)table[r * p.table_cols + p.taps.t[k < OC_MAX_TAPS ? k : 0]] : -1;
+      }
+    };
+    auto publish_indices = [&](int buf) -> uint32_t {
+      uint32_t m = 0;
+      int* dst = sidx + buf * (OC_MAX_TAPS * TILE_R);
+#pragma unroll
+      for (int i = 0; i < NF; ++i) {
+        const int k = 2 * i + fhalf;
+        if (k < OC_MAX_TAPS) {
+          dst[k * TILE_R + frow] = nidx[i];
+          m |= (nidx[i] >= 0 ? 1u : 0u) << k;
+        }
+      }
+      m = __reduce_or_sync(0xffffffffu, m);
+      if (lane == 0) misc[2 + pw + PROD_WARPS * buf] = m;
+      mbar_arrive(psync_bar);
+      if (!mbar_wait(psync_bar, psync_phase, abort_flag, &g_tc_status, 15)) ok = false;
+      psync_phase ^= 1u;
+      uint32_t all = 0;
+#pragma unroll
+      for (int w = 0; w < PROD_WARPS; ++w) all |= misc[2 + w + PROD_WARPS * buf];
+      return all;
+    };
+    // copies the 4 rows of this lane for one 64-channel block; rid < 0 -> zeros
+    auto gather_block = [&](uint32_t dst, const int (&rid)[4], int kb) {
+      const int kc = min(64, p.Cin - kb * 64);
+      if (chunk * 8 < kc) {
+        const uint8_t* lane_src = data + (size_t)kb * 128 + chunk * 16;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int idx = rid[j];
+          cp_async_16(dst + doff[j], lane_src + (size_t)(idx < 0 ? 0 : idx) * row_bytes, idx >= 0 ? 16u : 0u);
+        }
+      } else {
+        // channels past Cin would otherwise hold stale shared memory: they end up in
+        // accumulator rows that are never stored, but must not be NaN-producing garbage
+#pragma unroll
+        for (int j = 0; j < 4; ++j) cp_async_16(dst + doff[j], data, 0u);
+      }
+    };
+
+    int64_t tile = t_begin;
+    int buf = 0;
+    uint32_t mask = 0;
+    if (tile < t_end) {
+      fetch_indices(tile);
+      mask = publish_indices(buf);
+    }
+    for (; tile < t_end && ok; ++tile) {
+      const int64_t next = tile + 1;
+      if (next < t_end) fetch_indices(next);
+      const int* cur = sidx + buf * (OC_MAX_TAPS * TILE_R);
+      if (mask != 0) {
+        // ---- grad_out tile: dense rows, NTW columns, as GB swizzled 64-column blocks
+        if (!mbar_wait(gempty_bar(gb_sel), g_phase[gb_sel] ^ 1u, abort_flag, &g_tc_status, 11)) { ok = false; break; }
+        const uint32_t g_dst = s_base + L.gbuf + gb_sel * (uint32_t)(p.GB * BLK_BYTES);
+        for (int gb = 0; gb < p.GB; ++gb) {
+          const int col = n0 + gb * 64 + chunk * 8;
+          const bool col_ok = col < p.Cout && gb * 64 + chunk * 8 < p.NTW;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int64_t r = tile * TILE_R + row0 + j;
+            const bool v = col_ok && r < p.n_out;
+            cp_async_16(g_dst + gb * BLK_BYTES + doff[j], v ? gout + (size_t)r * grow_bytes + (size_t)col * 2 : gout,
+                        v ? 16u : 0u);
+          }
+        }
+        cp_async_arrive_noinc(gfull_bar(gb_sel));
+        g_phase[gb_sel] ^= 1u;
+        gb_sel ^= 1u;
+        // ---- one stage per M tile that has a valid tap in this row tile
+        int last_m = -1;
+        for (int m = 0; m < m_cnt; ++m) {
+          const int b0 = 2 * (m_lo + m), b1 = b0 + 1;
+          const bool v0 = (mask >> (b0 / p.KB)) & 1u;
+          const bool v1 = b1 < p.nblk && ((mask >> (b1 / p.KB)) & 1u);
+          if (v0 || v1) last_m = m;
+        }
+        bool first = true;
+        for (int m = 0; m <= last_m && ok; ++m) {
+          const int b0 = 2 * (m_lo + m), b1 = b0 + 1;
+          const int k0 = b0 / p.KB, k1 = b1 / p.KB;
+          const bool v0 = (mask >> k0) & 1u;
+          const bool v1 = b1 < p.nblk && ((mask >> k1) & 1u);
+          if (!(v0 || v1)) continue;
+          int rid0[4] = {-1, -1, -1, -1}, rid1[4] = {-1, -1, -1, -1};
+          if (v0) {
+            const int4 r4 = *reinterpret_cast<const int4*>(cur + k0 * TILE_R + row0);
+            rid0[0] = r4.x; rid0[1] = r4.y; rid0[2] = r4.z; rid0[3] = r4.w;
+          }
+          if (v1) {
+            const int4 r4 = *reinterpret_cast<const int4*>(cur + k1 * TILE_R + row0);
+            rid1[0] = r4.x; rid1[1] = r4.y; rid1[2] = r4.z; rid1[3] = r4.w;
+          }
+          if (!mbar_wait(empty_bar(s), ring_phase ^ 1u, abort_flag, &g_tc_status, 12)) { ok = false; break; }
+          const uint32_t a_dst = s_base + L.ring + s * (uint32_t)(2 * BLK_BYTES);
+          if (pt == 0) {
+            hdr[s] = (first ? 1u : 0u) | (m == last_m ? 2u : 0u) | (((touched >> m) & 1u) ? 0u : 8u) |
+                     ((uint32_t)m << 8);
+            mbar_arrive(full_bar(s));
+          }
+          touched |= 1u << m;
+          first = false;
+          gather_block(a_dst, rid0, b0 % p.KB);
+          gather_block(a_dst + BLK_BYTES, rid1, b1 < p.nblk ? b1 % p.KB : 0);
+          cp_async_arrive_noinc(full_bar(s));
+          if (++s == S) { s = 0; ring_phase ^= 1u; }
+        }
+      }
+      if (next < t_end) {
+        buf ^= 1;
+        mask = publish_indices(buf);
+      }
+    }
+    // end marker for the MMA warp
+    if (ok && mbar_wait(empty_bar(s), ring_phase ^ 1u, abort_flag, &g_tc_status, 13)) {
+      if (pt == 0) {
+        hdr[s] = 4u;
+        misc[18] = touched;
+        mbar_arrive(full_bar(s));
+      }
+      cp_async_arrive_noinc(full_bar(s));
+    }
+    cp_async_wait_all();
+  } else if (warp == MMA_WARP) {
+    // ===================================================================== MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(BF16 ? 1 : 0, 1, 1, 128, p.NTW);   // both operands MN-major
+      int s = 0;
+      uint32_t ring_phase = 0;
+      uint32_t gb_sel = 0, g_phase[2] = {0, 0};
+      bool issued_any = false;
+      for (;;) {
+        if (!mbar_wait(full_bar(s), ring_phase, abort_flag, &g_tc_status, 16)) break;
+        tc_fence_after();
+        const uint32_t h = hdr[s];
+        if (h & 4u) break;
+        if (h & 1u) {   // first stage of a row tile: its grad_out block must have landed
+          if (!mbar_wait(gfull_bar(gb_sel), g_phase[gb_sel], abort_flag, &g_tc_status, 17)) break;
+          tc_fence_after();
+        }
+        const uint32_t m = h >> 8;
+        const uint32_t a_addr = s_base + L.ring + s * (uint32_t)(2 * BLK_BYTES);
+        const uint32_t g_addr = s_base + L.gbuf + gb_sel * (uint32_t)(p.GB * BLK_BYTES);
+        const uint32_t d_tmem = tmem_base + m * (uint32_t)p.NTW;
+#pragma unroll
+        for (uint32_t ks = 0; ks < TILE_R / 16; ++ks) {
+          // MN-major, 128-byte swizzle: 64-element atoms along M / N are BLK_BYTES apart
+          // (leading offset), groups of 8 rows along K are 1024 B apart (stride offset)
+          const uint64_t da = make_desc_sw128(a_addr + ks * 2048, BLK_BYTES, 1024);
+          const uint64_t db = make_desc_sw128(g_addr + ks * 2048, BLK_BYTES, 1024);
+          umma_f16(d_tmem, da, db, idesc, ((h & 8u) && ks == 0) ? 0u : 1u);
+        }
+        issued_any = true;
+        umma_commit(empty_bar(s));
+        if (h & 2u) {   // last stage of the row tile: release the grad_out buffer
+          umma_commit(gempty_bar(gb_sel));
+          g_phase[gb_sel] ^= 1u;
+          gb_sel ^= 1u;
+        }
+        if (++s == S) { s = 0; ring_phase ^= 1u; }
+      }
+      (void)issued_any;
+      umma_commit(done_bar);
+      mbar_wait(done_bar, 0, abort_flag, &g_tc_status, 18);   // all MMAs retired
+    }
+    __syncwarp();
+  }
+  // warps 0-3 have no role in the main loop: they wait here without polling.
+
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) {}
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  // ------------------------------------------------------------------------ epilogue
+  // Warp w reads TMEM lanes 32*(w%4).. of the M tiles m = w/4, w/4 + 3, ... (warps 0-11).
+  if (warp < 12 && !*abort_flag) {
+    const uint32_t touched = misc[18];
+    const int q = warp & 3;
+    const int mrow = q * 32 + lane;                    // row of the M tile = (block half, channel)
+    for (int m = warp >> 2; m < m_cnt; m += 3) {
+      const int b = 2 * (m_lo + m) + (mrow >> 6);
+      const int k = b / p.KB, kb = b % p.KB;
+      const int ci = kb * 64 + (mrow & 63);
+      const bool row_ok = b < p.nblk && ci < p.Cin;
+      const bool has = (touched >> m) & 1u;
+      float* dst = p.partial + (((int64_t)slice * p.K + (row_ok ? k : 0)) * p.Cin + (row_ok ? ci : 0)) * p.Cout + n0;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + m * (uint32_t)p.NTW;
+      for (int c0 = 0; c0 < p.NTW; c0 += 16) {
+        uint32_t r[16];
+        if (has) {          // warp-uniform
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = 0u;
+        }
+        if (row_ok && n0 + c0 < p.Cout) {
+          float4* d4 = (float4*)(dst + c0);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            d4[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                __uint_as_float(r[4 * j + 3]));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+
+struct Plan {
+  int KB, nblk, n_mt, NTW, GB, n_tiles_n, mt_per_cta, groups, stages, tmem_cols, slices;
+  int64_t tiles_per_slice;
+  uint32_t smem_bytes;
+  bool ok;
+};
+
+static Plan make_plan(int K, int Cin, int Cout, int64_t n_out, int dtype) {
+  Plan P = {};
+  P.ok = false;
+  if (!(dtype == OC_F16 || dtype == OC_BF16)) return P;
+  if (Cin < 16 || Cin % 16 != 0 || Cout < 16 || Cout % 16 != 0) return P;
+  if (K < 1 || K > OC_MAX_TAPS) return P;
+  P.KB = (Cin + 63) / 64;
+  P.nblk = K * P.KB;
+  P.n_mt = (P.nblk + 1) / 2;
+  P.n_tiles_n = (Cout + 127) / 128;
+  P.NTW = Cout <= 128 ? Cout : 128;
+  P.GB = (P.NTW + 63) / 64;
+  P.mt_per_cta = 512 / P.NTW;
+  if (P.mt_per_cta > MAX_MT) P.mt_per_cta = MAX_MT;
+  if (P.mt_per_cta > P.n_mt) P.mt_per_cta = P.n_mt;
+  P.groups = (P.n_mt + P.mt_per_cta - 1) / P.mt_per_cta;
+  // balance the groups
+  P.mt_per_cta = (P.n_mt + P.groups - 1) / P.groups;
+  P.tmem_cols = 32;
+  while (P.tmem_cols < P.mt_per_cta * P.NTW) P.tmem_cols *= 2;
+  if (P.tmem_cols > 512) return P;
+  const uint32_t budget = 227 * 1024 - 1024;
+  int stages = MAX_STAGES;
+  while (stages > 2 && smem_layout(P.GB, stages).total > budget) --stages;
+  if (smem_layout(P.GB, stages).total > budget) return P;
+  P.stages = stages;
+  P.smem_bytes = smem_layout(P.GB, stages).total + 1024;
+  const int64_t n_tiles = cdiv(n_out > 0 ? n_out : 1, TILE_R);
+  int64_t slices = sm_count() / (P.groups * P.n_tiles_n);
+  if (slices < 1) slices = 1;
+  if (slices > n_tiles) slices = n_tiles;
+  P.tiles_per_slice = cdiv(n_tiles, slices);
+  P.slices = (int)cdiv(n_tiles, P.tiles_per_slice);
+  P.ok = true;
+  return P;
+}
+
+}  // namespace wg
+
+bool wgrad_tc_supported(int K, int Cin, int Cout, int dtype) { return wg::make_plan(K, Cin, Cout, 1, dtype).ok; }
+
+size_t wgrad_tc_workspace_bytes(int K, int Cin, int Cout, int64_t n_out) {
+  const wg::Plan P = wg::make_plan(K, Cin, Cout, n_out, OC_F16);
+  return align_up((size_t)P.slices * K * Cin * Cout * sizeof(float), 256);
+}
+
+template <bool BF16, typename I>
+static int launch_wgrad_tc_t(const wg::Params& prm, const wg::Plan& P, cudaStream_t s) {
+  auto kern = wg::wgrad_tc_kernel<BF16, I>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  OC_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    OC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured_dev = dev;
+  }
+  dim3 grid((unsigned)P.slices, (unsigned)P.groups, (unsigned)P.n_tiles_n);
+  kern<<<grid, wg::THREADS, P.smem_bytes, s>>>(prm);
+  OC_LAUNCH_OK("wgrad_tc_kernel");
+  return OC_OK;
+}
+
+int launch_wgrad_tc(const WgradArgs& a, float* grad_w, void* workspace, size_t workspace_bytes, cudaStream_t s) {
+  const wg::Plan P = wg::make_plan(a.K, a.Cin, a.Cout, a.n_out, a.dtype);
+  OC_REQUIRE(P.ok, OC_EINVAL, "wgrad_tc: unsupported shape");
+  const size_t need = (size_t)P.slices * a.K * a.Cin * a.Cout * sizeof(float);
+  OC_REQUIRE(workspace && workspace_bytes >= need, OC_ENOMEM, "wgrad_tc: workspace %zu < %zu", workspace_bytes, need);
+  OC_REQUIRE(((uintptr_t)a.data % 16) == 0 && ((uintptr_t)a.grad_out % 16) == 0 && ((uintptr_t)workspace % 16) == 0,
+             OC_EINVAL, "wgrad_tc: data, grad_out and workspace must be 16-byte aligned");
+  wg::Params prm;
+  prm.data = a.data; prm.gout = a.grad_out; prm.table = a.table; prm.partial = (float*)workspace;
+  prm.n_out = a.n_out; prm.tiles_per_slice = P.tiles_per_slice; prm.table_cols = a.table_cols;
+  prm.K = a.K; prm.Cin = a.Cin; prm.Cout = a.Cout; prm.KB = P.KB; prm.nblk = P.nblk; prm.NTW = P.NTW;
+  prm.GB = P.GB; prm.mt_per_cta = P.mt_per_cta; prm.stages = P.stages; prm.tmem_cols = P.tmem_cols;
+  prm.taps = a.taps;
+  const bool bf = a.dtype == OC_BF16;
+  int rc;
+  if (a.idx_bytes == 8) rc = bf ? launch_wgrad_tc_t<true, int64_t>(prm, P, s) : launch_wgrad_tc_t<false, int64_t>(prm, P, s);
+  else rc = bf ? launch_wgrad_tc_t<true, int32_t>(prm, P, s) : launch_wgrad_tc_t<false, int32_t>(prm, P, s);
+  if (rc) return rc;
+  return reduce_partials((const float*)workspace, P.slices, (int64_t)a.K * a.Cin * a.Cout, grad_w, s);
+}
+
+}  // namespace oc
