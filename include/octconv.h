@@ -230,6 +230,22 @@ int oc_upsample_bwd(const void* grad_out, const int32_t* children_coarse,
 size_t oc_colstats_workspace_bytes(int64_t n, int C);
 int oc_colstats(const void* a, const void* b, int64_t n, int C, int dtype, float* sum_a,
                 float* sum_ab, void* workspace, size_t workspace_bytes, void* stream);
+/* Same sums as oc_colstats, for callers that have no way to supply a workspace
+ * and must not trigger an allocation: hosts whose start-up code reserved the whole
+ * GPU for their own arena, or plugin code that only ever sees raw pointers.  The
+ * per-block partials go to a 2 MiB array built into the library (every GPU that
+ * loads the library keeps that array until the process exits).  Nothing here calls
+ * cudaMalloc / cudaFree or any allocating routine.
+ *   - Limit: C <= 4096; a larger C is refused with OC_EINVAL and a message that
+ *     points to oc_colstats.  The number of row slices shrinks as C grows.
+ *   - The first call on each device looks up the array's device address (with
+ *     that device current); make that first call outside any stream capture.
+ *   - All calls share the one array, which still holds the previous call's
+ *     partials; each call overwrites every slot it later reads, so no clearing is
+ *     needed, but two calls that overlap on the GPU (different streams) race.
+ * No counterpart in the reference: it exists only for these callers. */
+int oc_colstats_static(const void* a, const void* b, int64_t n, int C, int dtype, float* sum_a,
+                       float* sum_ab, void* stream);
 /* out[n,c] = x[n,c] * scale[c] + shift[c]   (scale/shift fp32) */
 int oc_affine_cols(const void* x, const float* scale, const float* shift, int64_t n, int C,
                    int dtype, void* out, void* stream);

@@ -59,6 +59,7 @@ PROTOTYPES = {
     'oc_upsample_bwd': (_i, [_vp, _vp, _vp, _i64, _i, _i, _vp, _vp]),
     'oc_colstats_workspace_bytes': (_sz, [_i64, _i]),
     'oc_colstats': (_i, [_vp, _vp, _i64, _i, _i, _vp, _vp, _vp, _sz, _vp]),
+    'oc_colstats_static': (_i, [_vp, _vp, _i64, _i, _i, _vp, _vp, _vp]),
     'oc_affine_cols': (_i, [_vp, _vp, _vp, _i64, _i, _i, _vp, _vp]),
     'oc_bn_bwd_apply': (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _vp, _vp]),
     'oc_gn_workspace_bytes': (_sz, [_i, _i]),

@@ -7,6 +7,8 @@
 // ranges instead of three atomic scatter_adds.  All reductions are two-stage
 // (per-block partials in a workspace, then a fixed-order sum): no atomics, so
 // results are reproducible run to run.
+#include <mutex>
+
 #include "oc_common.cuh"
 #include "conv_internal.cuh"
 
@@ -329,6 +331,77 @@ extern "C" int oc_colstats(const void* a, const void* b, int64_t n, int C, int d
   OC_REQUIRE(dtype == OC_F32 || dtype == OC_F16 || dtype == OC_BF16, OC_EINVAL, "oc_colstats: bad dtype");
   OC_REQUIRE(n >= 0 && C >= 1 && (n == 0 || a), OC_EINVAL, "oc_colstats: bad argument");
   return launch_colstats(a, b, n, C, dtype, sum_a, sum_ab, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------
+// Column statistics without any workspace: the per-block partial sums live in a
+// fixed array that is part of the library image.
+//
+// Meant for hosts that hand the whole device to an arena of their own at start-up
+// (an inference server, a trainer with a locked pool) and for plugin callers that
+// are handed raw pointers and no allocator at all: there a cudaMalloc inside the
+// step either fails or stalls every stream of the process, and there is nobody to
+// ask for a workspace.  The price is a hard size limit and one shared buffer.
+// ---------------------------------------------------------------------------
+constexpr int STATIC_STATS_MAX_C = 4096;
+constexpr size_t STATIC_STATS_FLOATS = 512 * 1024;   // 2 MiB, resident on every GPU that loads the library
+static __device__ __align__(256) float g_static_stats[STATIC_STATS_FLOATS];
+
+// The array name is only a host-side handle; kernels need its device address, which
+// differs per GPU.  Resolved once per device, with that device current.
+static int static_stats_address(float** out) {
+  static std::mutex mu;
+  static float* per_device[64] = {nullptr};
+  int dev = 0;
+  OC_CUDA_OK(cudaGetDevice(&dev));
+  OC_REQUIRE(dev >= 0 && dev < 64, OC_EINVAL, "oc_colstats_static: device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!per_device[dev]) {
+    void* p = nullptr;
+    OC_CUDA_OK(cudaGetSymbolAddress(&p, g_static_stats));
+    OC_REQUIRE(p != nullptr, OC_ECUDA, "oc_colstats_static: null symbol address");
+    per_device[dev] = (float*)p;
+  }
+  *out = per_device[dev];
+  return OC_OK;
+}
+
+extern "C" int oc_colstats_static(const void* a, const void* b, int64_t n, int C, int dtype, float* sum_a,
+                                  float* sum_ab, void* stream) {
+  OC_REQUIRE(dtype == OC_F32 || dtype == OC_F16 || dtype == OC_BF16, OC_EINVAL, "oc_colstats_static: bad dtype");
+  OC_REQUIRE(C >= 1 && C <= STATIC_STATS_MAX_C, OC_EINVAL,
+             "oc_colstats_static: C = %d exceeds the built-in scratch limit of %d channels; use oc_colstats with "
+             "a caller-provided workspace", C, STATIC_STATS_MAX_C);
+  OC_REQUIRE(n >= 0 && n < (1LL << 40), OC_EINVAL, "oc_colstats_static: row count out of range");
+  OC_REQUIRE(n == 0 || a, OC_EINVAL, "oc_colstats_static: null input");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (n == 0) {
+    if (sum_a) OC_CUDA_OK(cudaMemsetAsync(sum_a, 0, (size_t)C * 4, s));
+    if (sum_ab) OC_CUDA_OK(cudaMemsetAsync(sum_ab, 0, (size_t)C * 4, s));
+    return OC_OK;
+  }
+  float* scratch = nullptr;
+  int rc = static_stats_address(&scratch);
+  if (rc) return rc;
+  // As many row slices as fit: two partial rows of C floats per slice.  Every slot
+  // that the final pass reads is written by this launch, so stale contents of the
+  // shared array never matter and nothing has to be cleared.
+  int splits = cs_splits(n);
+  const int64_t cap = (int64_t)(STATIC_STATS_FLOATS / (2 * (size_t)C));
+  if (splits > cap) splits = (int)cap;
+  float* pa = scratch;
+  float* pab = scratch + (size_t)splits * C;
+  const int64_t rps = cdiv(n, splits);
+  const int CT = cs_ct(C);
+  if (dtype == OC_F32)
+    colstats_kernel<float><<<splits, CS_THREADS, 0, s>>>((const float*)a, (const float*)b, 0, n, rps, C, CT, pa, pab);
+  else if (dtype == OC_F16)
+    colstats_kernel<__half><<<splits, CS_THREADS, 0, s>>>((const __half*)a, (const __half*)b, 0, n, rps, C, CT, pa, pab);
+  else
+    colstats_kernel<__nv_bfloat16><<<splits, CS_THREADS, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, 0, n, rps, C, CT, pa, pab);
+  colstats_final_kernel<<<(unsigned)cdiv(C, 128), 128, 0, s>>>(pa, pab, splits, C, sum_a, sum_ab);
+  OC_LAUNCH_OK("colstats kernels (static scratch)");
+  return OC_OK;
 }
 
 extern "C" int oc_affine_cols(const void* x, const float* scale, const float* shift, int64_t n, int C,
