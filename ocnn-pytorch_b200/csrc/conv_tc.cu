@@ -39,6 +39,7 @@ constexpr int KBLK = 64;                 // channels per K block = one 128-byte 
 constexpr int A_BYTES = TILE_M * 128;    // 16 KB
 constexpr int PROD_WARPS = 8;             // warps 4..11 gather; warp 12 issues the MMAs
 constexpr int PROD_THREADS = PROD_WARPS * 32;
+constexpr int FSPLIT = PROD_THREADS / TILE_M;    // threads that share the index prefetch of one row
 constexpr int MMA_WARP = 4 + PROD_WARPS;
 constexpr int THREADS = (MMA_WARP + 1) * 32;
 constexpr int MAX_STAGES = 8;
@@ -73,7 +74,7 @@ __host__ __device__ inline SmemLayout smem_layout(int NT, int stages) {
   L.bars = L.bias + MAX_NT * 4;
   L.hdr = L.bars + (2 * MAX_STAGES + 5) * 8;
   L.misc = L.hdr + MAX_STAGES * 4;
-  L.total = L.misc + 128;
+  L.total = L.misc + 256;
   return L;
 }
 
@@ -108,7 +109,7 @@ conv_tc_kernel(const Params p) {
   float* sbias = (float*)(smem + L.bias);
   const uint32_t bars = s_base + L.bars;
   volatile uint32_t* hdr = (volatile uint32_t*)(smem + L.hdr);
-  uint32_t* misc = (uint32_t*)(smem + L.misc);   // [0] tmem base, [1] abort flag, [2..17] warp masks (2 buffers)
+  uint32_t* misc = (uint32_t*)(smem + L.misc);   // [0] tmem base, [1] abort flag, [2..] warp masks (2 buffers x PROD_WARPS)
   volatile int* abort_flag = (volatile int*)(misc + 1);
 
   const int S = p.stages;
@@ -124,7 +125,7 @@ conv_tc_kernel(const Params p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(full_bar(s), PROD_THREADS + 1);   // every producer thread's copies + 1 arrive.expect_tx (weights)
+      mbar_init(full_bar(s), 32 + 1);   // the 32 lanes of the owning warp + 1 arrive.expect_tx (weights)
       mbar_init(empty_bar(s), 1);    // one tcgen05.commit
     }
     for (int a = 0; a < 2; ++a) {
@@ -154,23 +155,25 @@ conv_tc_kernel(const Params p) {
     // ===================================================================== producers
     const int pt = threadIdx.x - 128;          // 0..255
     const int pw = warp - 4;
-    const int frow = pt & (TILE_M - 1);        // index prefetch: row `frow`, taps of parity `fhalf`
-    const int fhalf = pt >> 7;
+    const int frow = pt & (TILE_M - 1);        // index prefetch: row `frow`, taps k = fpart (mod FSPLIT)
+    const int fpart = pt >> 7;
     const I* table = (const I*)p.table;
     const uint8_t* data = (const uint8_t*)p.data;
     const uint32_t row_bytes = (uint32_t)p.Cin * 2;
     const uint8_t* wimg = (const uint8_t*)p.wimg + (size_t)blockIdx.y * p.K * p.KB * (size_t)(p.NT * 128);
     const uint32_t b_bytes = (uint32_t)p.NT * 128;
-    // gather mapping: 8 lanes copy one 128-byte row (16 B each); a lane owns 4
-    // consecutive rows of its warp's 16, so their indices come with one 16-byte load
+    // Stages are dealt to the producer warps round-robin: a whole stage (128 rows x 8
+    // chunks of 16 B) is copied by one warp, so the per-stage bookkeeping (slot wait,
+    // header, weight copy, barrier arrival) is paid by one warp while the others work on
+    // their own stages.  8 lanes copy one 128-byte row; lane group g = lane / 8 owns the
+    // rows 32 g .. 32 g + 31 of the tile, fetched 4 indices at a time.
     const int chunk = lane & 7;
-    const int row0 = pw * 16 + (lane >> 3) * 4;
-    uint32_t doff[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) doff[j] = (uint32_t)((row0 + j) * 128 + ((chunk ^ ((row0 + j) & 7)) << 4));
+    const int grp = lane >> 3;
+    const int n_own = S < PROD_WARPS ? S : PROD_WARPS;   // warps that own stages (a warp needs a slot of its own)
+    uint32_t gstage = 0;                       // running stage number of this CTA (same in every warp)
     int s = 0;                                 // ring slot of the next stage
     uint32_t ring_phase = 0;                   // flips each time the ring wraps
-    constexpr int NF = (OC_MAX_TAPS + 1) / 2;
+    constexpr int NF = (OC_MAX_TAPS + FSPLIT - 1) / FSPLIT;
     int nidx[NF];
     bool ok = true;
     uint32_t psync_phase = 0;
@@ -179,7 +182,7 @@ conv_tc_kernel(const Params p) {
       const int64_t r = tile * TILE_M + frow;
 #pragma unroll
       for (int i = 0; i < NF; ++i) {
-        const int k = 2 * i + fhalf;
+        const int k = FSPLIT * i + fpart;
         nidx[i] = (k < p.K && r < p.n_out) ? (int)table[r * p.table_cols + p.taps.t[k < OC_MAX_TAPS ? k : 0]] : -1;
       }
     };
@@ -188,7 +191,7 @@ conv_tc_kernel(const Params p) {
       int* dst = sidx + buf * (OC_MAX_TAPS * TILE_M);
 #pragma unroll
       for (int i = 0; i < NF; ++i) {
-        const int k = 2 * i + fhalf;
+        const int k = FSPLIT * i + fpart;
         if (k < OC_MAX_TAPS) {
           dst[k * TILE_M + frow] = nidx[i];
           m |= (nidx[i] >= 0 ? 1u : 0u) << k;
@@ -222,30 +225,39 @@ conv_tc_kernel(const Params p) {
       const uint32_t first_k = __ffs(mask) - 1;
       for (uint32_t k = first_k; k <= last_k && ok; ++k) {
         if (!((mask >> k) & 1u)) continue;
-        // the 4 row indices of this lane for tap k: read before any copy is issued
-        const int4 r4 = *reinterpret_cast<const int4*>(cur + k * TILE_M + row0);
-        const int rid[4] = {r4.x, r4.y, r4.z, r4.w};
         for (int kb = 0; kb < p.KB; ++kb) {
-          if (!mbar_wait(empty_bar(s), ring_phase ^ 1u, abort_flag, &g_tc_status, 1)) { ok = false; break; }
-          const uint32_t a_dst = s_base + L.ring + s * L.stage_bytes;
-          const int kc = min(KBLK, p.Cin - kb * KBLK);          // channels in this block
-          if (pt == 0) {
-            hdr[s] = (k == first_k && kb == 0 ? 1u : 0u) | (k == last_k && kb == p.KB - 1 ? 2u : 0u) |
-                     ((uint32_t)(kc / 16) << 8);
-            mbar_arrive_expect_tx(full_bar(s), b_bytes);
-            bulk_g2s(a_dst + A_BYTES, wimg + ((size_t)k * p.KB + kb) * b_bytes, b_bytes, full_bar(s));
-          }
-          if (chunk * 8 < kc) {
-            const uint8_t* lane_src = data + (size_t)kb * 128 + chunk * 16;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int idx = rid[j];
-              cp_async_16(a_dst + doff[j], lane_src + (size_t)(idx < 0 ? 0 : idx) * row_bytes, idx >= 0 ? 16u : 0u);
+          const bool mine = (int)(gstage % (uint32_t)n_own) == pw;
+          ++gstage;
+          if (mine) {
+            if (!mbar_wait(empty_bar(s), ring_phase ^ 1u, abort_flag, &g_tc_status, 1)) { ok = false; break; }
+            const uint32_t a_dst = s_base + L.ring + s * L.stage_bytes;
+            const int kc = min(KBLK, p.Cin - kb * KBLK);          // channels in this block
+            if (lane == 0) {
+              hdr[s] = (k == first_k && kb == 0 ? 1u : 0u) | (k == last_k && kb == p.KB - 1 ? 2u : 0u) |
+                       ((uint32_t)(kc / 16) << 8);
+              mbar_arrive_expect_tx(full_bar(s), b_bytes);
+              bulk_g2s(a_dst + A_BYTES, wimg + ((size_t)k * p.KB + kb) * b_bytes, b_bytes, full_bar(s));
             }
+            if (chunk * 8 < kc) {
+              const uint8_t* lane_src = data + (size_t)kb * 128 + chunk * 16;
+              const int* irow = cur + k * TILE_M + grp * 32;
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const int4 r4 = *reinterpret_cast<const int4*>(irow + 4 * q);
+                const int rid[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int r = grp * 32 + 4 * q + j;            // (r & 7) == (4 q + j) & 7: known at compile time
+                  const int idx = rid[j];
+                  cp_async_16(a_dst + r * 128 + ((chunk ^ ((4 * q + j) & 7)) << 4),
+                              lane_src + (size_t)(idx < 0 ? 0 : idx) * row_bytes, idx >= 0 ? 16u : 0u);
+                }
+              }
+            }
+            // arrives on the stage's barrier once this lane's copies have landed; the lane
+            // itself does not wait, so every warp keeps a whole stage in flight
+            cp_async_arrive_noinc(full_bar(s));
           }
-          // arrives on the stage's barrier once this thread's copies have landed; the
-          // thread itself does not wait, so up to `stages` gathers stay in flight
-          cp_async_arrive_noinc(full_bar(s));
           if (++s == S) { s = 0; ring_phase ^= 1u; }
         }
       }
