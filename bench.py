@@ -195,6 +195,8 @@ def run_ours(args):
   torch.cuda.synchronize()
   if args.mode == 'conv':
     return run_conv_only(args, b200, octree, dev)
+  if args.mode == 'suite':
+    return run_suite(args, b200, octree, dev)
   # octree build throughput (secondary figure): host points -> octree + all neighbour tables
   t_build = []
   for i in range(3):
@@ -372,6 +374,125 @@ def run_conv_only(args, b200, octree, dev):
   print(json.dumps(out))
 
 
+def _time(fn, reps=10, warm=3):
+  import torch
+  for _ in range(warm):
+    fn()
+  torch.cuda.synchronize()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for _ in range(reps):
+    fn()
+  e1.record()
+  torch.cuda.synchronize()
+  return e0.elapsed_time(e1) / reps
+
+
+def run_suite(args, b200, octree, dev):
+  """Secondary measurements: every kernel family of the path on the benchmark batch, one JSON
+  line each (ms, achieved TFLOP/s or GB/s from algorithmic work, fraction of the measured peak)."""
+  import torch
+  pk = peaks()
+  g = torch.Generator(device=dev).manual_seed(0)
+  D = DEPTH
+
+  def emit(name, ms, flops=None, nbytes=None, **kw):
+    o = {'op': name, 'ms': round(ms, 4)}
+    if flops is not None:
+      o['tflops'] = round(flops / ms / 1e9, 2)
+      o['frac_tensor_peak'] = round(flops / ms / 1e9 / pk['tflops'], 4)
+    if nbytes is not None:
+      o['gbs'] = round(nbytes / ms / 1e6, 1)
+      o['frac_hbm_peak'] = round(nbytes / ms / 1e6 / pk['hbm'], 4)
+    o.update(kw)
+    print(json.dumps(o), flush=True)
+
+  for nempty in (False, True):
+    n = int(octree.nnum_nempty[D] if nempty else octree.nnum[D])
+    table, taps = octree.conv_table(D, '333', 1, nempty)
+    table_t, taps_t = octree.conv_table_transposed(D, '333', 1, nempty)
+    nnz = int((table >= 0).sum().item())
+    for dtype in (torch.float16, torch.bfloat16):
+      for C in (32, 64, 128, 256):
+        if dtype == torch.bfloat16 and C not in (64, 256):
+          continue
+        x = torch.randn(n, C, device=dev, generator=g).to(dtype)
+        gy = torch.randn(n, C, device=dev, generator=g).to(dtype)
+        w = (torch.randn(27, C, C, device=dev, generator=g) / (27 * C) ** 0.5)
+        fl = 2.0 * nnz * C * C
+        tag = dict(C=C, dtype=str(dtype).split('.')[-1], nempty=nempty, rows=n, valid_taps=nnz)
+        emit('conv333_fwd', _time(lambda: b200.nn.conv_gather(x, w, False, None, table, taps, C, C)), flops=fl, **tag)
+        emit('conv333_dgrad', _time(lambda: b200.nn.conv_gather(gy, w, True, None, table_t, taps_t, C, C)), flops=fl, **tag)
+        emit('conv333_wgrad', _time(lambda: b200.nn.conv_wgrad(x, gy, table, taps, C, C)), flops=fl, **tag)
+        del x, gy
+  # strided / transposed path (bf16), depth-wise conv, pooling, upsampling, normalisation
+  n8, n7 = int(octree.nnum[D]), int(octree.nnum[D - 1])
+  for ks in ([3], [2]):
+    conv = b200.nn.OctreeConv(64, 128, ks, 2, False).to(dev).bfloat16()
+    deconv = b200.nn.OctreeDeconv(128, 64, ks, 2, False).to(dev).bfloat16()
+    x = torch.randn(n8, 64, device=dev, generator=g).bfloat16().requires_grad_()
+    gy = torch.randn(n8, 64, device=dev, generator=g).bfloat16()
+
+    def step():
+      x.grad = None
+      y = deconv(conv(x, octree, D), octree, D - 1)
+      y.backward(gy)
+    tb, _ = octree.conv_table(D, '333' if ks == [3] else '222', 2, False)
+    nz = int((tb >= 0).sum().item())
+    emit('conv_s2_64to128 + deconv_s2_128to64 fwd+bwd (bf16, kernel %s)' % ks, _time(step, 5, 2),
+         flops=2 * 3 * 2.0 * nz * 64 * 128, rows_fine=n8, rows_coarse=n7, valid_taps=nz)
+    del x, gy
+  C = 256
+  s = 2
+  x = torch.randn(n8, C, device=dev, generator=g).half()
+  dw = b200.nn.OctreeDWConv(C, [3]).to(dev)
+  table, taps = octree.conv_table(D, '333', 1, False)
+  emit('dwconv333_fwd C=256 fp16', _time(lambda: dw(x, octree, D)), nbytes=2 * n8 * C * s + n8 * 27 * 8, rows=n8)
+  emit('maxpool_fwd C=256 fp16', _time(lambda: b200.nn.octree_max_pool(x, octree, D)),
+       nbytes=(n8 + n7) * C * s + int(octree.nnum_nempty[D - 1]) * C * 8, rows=n8)
+  xc = torch.randn(n7, C, device=dev, generator=g).half()
+  emit('upsample_nearest_fwd C=256 fp16', _time(lambda: b200.nn.octree_nearest_upsample(xc, octree, D - 1)),
+       nbytes=(int(octree.nnum_nempty[D - 1]) + n8) * C * s, rows=n8)
+  bn = b200.nn.OctreeBatchNorm(C).to(dev)
+  emit('batchnorm_fwd (train) C=256 fp16', _time(lambda: bn(x)), nbytes=3 * n8 * C * s, rows=n8)
+  gn = b200.nn.OctreeGroupNorm(C, 32).to(dev)
+  emit('groupnorm_fwd C=256 fp16', _time(lambda: gn(x, octree, D)), nbytes=4 * n8 * C * s, rows=n8)
+  idx = octree.nempty_index(D)
+  xne = torch.randn(idx.numel(), C, device=dev, generator=g).half()
+  emit('octree_pad C=256 fp16', _time(lambda: b200.nn.octree_pad(xne, octree, D)), nbytes=(idx.numel() + n8) * C * s)
+  del x, xc, xne
+  # octree construction: config 4 shape (200k points per cloud, depth 10), bounded to 16 clouds
+  import ocnn_pytorch_b200 as B
+  nb, npts, depth = 16, 200000, 10
+  clouds = [B.synthetic.mixed_cloud(4000 + i, npts, jitter=0.005) for i in range(nb)]
+  pts = torch.from_numpy(np.concatenate([c[0] for c in clouds])).to(dev)
+  nrm = torch.from_numpy(np.concatenate([c[1] for c in clouds])).to(dev)
+  feat = torch.randn(nb * npts, 3, device=dev, generator=g)
+  bid = torch.from_numpy(np.concatenate([np.full(npts, i, np.float32) for i in range(nb)])).to(dev)
+  holder = {}
+
+  def build_only():
+    pc = B.Points(pts, nrm, feat, batch_id=bid, batch_size=nb)
+    o = B.Octree(depth, 3, nb, dev)
+    o.build_octree(pc)
+    holder['o'] = o
+
+  def neigh_only():
+    holder['o'].construct_all_neigh()
+  t_b = _time(build_only, 3, 1)
+  t_n = _time(neigh_only, 3, 1)
+  o = holder['o']
+  P = nb * npts
+  nn_ = [int(v) for v in o.nnum]
+  passes = (3 * depth + 4 + 7) // 8
+  build_bytes = P * (12 + 12 + 12) + P * 12 * 2 * passes + sum(nn_) * 12 + int(o.nnum_nempty[depth]) * 36
+  neigh_bytes = sum(nn_[1:]) * 27 * 8 + sum(nn_[:-1]) * (27 * 8 + 4)
+  emit('build_octree depth10 (16 x 200k pts, device resident)', t_b, nbytes=build_bytes, mpts_per_s=round(P / t_b / 1e3, 1), nnum=nn_)
+  emit('construct_all_neigh depth10', t_n, nbytes=neigh_bytes, mpts_per_s=round(P / t_n / 1e3, 1))
+  emit('build + neigh depth10', t_b + t_n, nbytes=build_bytes + neigh_bytes, mpts_per_s=round(P / (t_b + t_n) / 1e3, 1))
+  b200._lib.status_check(dev)
+
+
 def main():
   global BATCH
   ap = argparse.ArgumentParser()
@@ -382,7 +503,7 @@ def main():
   ap.add_argument('--batch', type=int, default=BATCH,
                   help='octrees per rank (default 16 = the benchmark configuration; smaller values '
                        'are for profiler captures)')
-  ap.add_argument('--mode', default='full', choices=['full', 'conv'],
+  ap.add_argument('--mode', default='full', choices=['full', 'conv', 'suite'],
                   help="'conv' runs only the timed conv steps (no build timing, e2e or CPU baseline)")
   args = ap.parse_args()
   BATCH = args.batch

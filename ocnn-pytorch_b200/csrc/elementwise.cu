@@ -76,6 +76,77 @@ __global__ void dwconv_kernel(const T* __restrict__ data, const float* __restric
   }
 }
 
+
+// Same computation with the per-block staging that makes it bandwidth-efficient:
+// the (K, C) weights sit in shared memory as fp32 for the whole block, the K neighbour
+// indices of the block's rows are fetched once (coalesced) instead of once per thread,
+// and each thread then streams its 16-byte channel slice of every valid neighbour row.
+template <typename T, typename I>
+__global__ void __launch_bounds__(256)
+dwconv_staged_kernel(const T* __restrict__ data, const float* __restrict__ w, const I* __restrict__ table,
+                     int table_cols, TapList taps, int K, int64_t n_out, int C, int rows_per_block,
+                     T* __restrict__ out) {
+  constexpr int N = 16 / sizeof(T);
+  extern __shared__ __align__(16) float dsm[];
+  float* sw = dsm;                               // [K][C]
+  int* sidx = (int*)(dsm + (size_t)K * C);       // [rows_per_block][K]
+  for (int i = threadIdx.x; i < K * C; i += blockDim.x) sw[i] = w[i];
+  const int cpr = C / N;
+  const int r_local = threadIdx.x / cpr;
+  const int c0 = (threadIdx.x % cpr) * N;
+  const bool active = r_local < rows_per_block;
+  const int64_t n_blocks = (n_out + rows_per_block - 1) / rows_per_block;
+  for (int64_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x) {
+    const int64_t row_base = blk * rows_per_block;
+    __syncthreads();                             // weights ready / previous indices consumed
+    for (int i = threadIdx.x; i < rows_per_block * K; i += blockDim.x) {
+      const int64_t r = row_base + i / K;
+      sidx[i] = r < n_out ? (int)table[r * table_cols + taps.t[i % K]] : -1;
+    }
+    __syncthreads();
+    const int64_t r = row_base + r_local;
+    if (!active || r >= n_out) continue;
+    float acc[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) acc[i] = 0.f;
+    const int* my = sidx + r_local * K;
+    for (int k = 0; k < K; ++k) {
+      const int idx = my[k];
+      if (idx < 0) continue;
+      const uint4 raw = *reinterpret_cast<const uint4*>(data + (int64_t)idx * C + c0);
+      const T* e = reinterpret_cast<const T*>(&raw);
+      const float4* wk = reinterpret_cast<const float4*>(sw + k * C + c0);
+#pragma unroll
+      for (int q = 0; q < N / 4; ++q) {
+        const float4 wv = wk[q];
+        acc[4 * q + 0] = fmaf(to_f32<T>(e[4 * q + 0]), wv.x, acc[4 * q + 0]);
+        acc[4 * q + 1] = fmaf(to_f32<T>(e[4 * q + 1]), wv.y, acc[4 * q + 1]);
+        acc[4 * q + 2] = fmaf(to_f32<T>(e[4 * q + 2]), wv.z, acc[4 * q + 2]);
+        acc[4 * q + 3] = fmaf(to_f32<T>(e[4 * q + 3]), wv.w, acc[4 * q + 3]);
+      }
+    }
+    RowIO<T, true>::store(out + r * C + c0, acc);
+  }
+}
+
+template <typename T, typename I>
+static bool launch_dwconv_staged(const void* data, const float* weights, const void* table, int table_cols,
+                                 const TapList& taps, int K, int64_t n_out, int C, void* out, cudaStream_t s) {
+  constexpr int N = 16 / sizeof(T);
+  const int cpr = C / N;
+  if (cpr > 256) return false;
+  const int rpb = 256 / cpr;
+  const size_t smem = (size_t)K * C * 4 + (size_t)rpb * K * 4;
+  if (smem > 200 * 1024) return false;
+  auto kern = dwconv_staged_kernel<T, I>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  const int64_t n_blocks = (n_out + rpb - 1) / rpb;
+  const int64_t cap = (int64_t)sm_count() * (smem > 64 * 1024 ? 2 : 6);
+  kern<<<(unsigned)(n_blocks < cap ? n_blocks : cap), 256, smem, s>>>((const T*)data, weights, (const I*)table, table_cols,
+                                                                     taps, K, n_out, C, rpb, (T*)out);
+  return true;
+}
+
 // grad_w partials: block (x = channel block, y = row split); thread = channel.
 template <typename T, typename I>
 __global__ void dwconv_wgrad_kernel(const T* __restrict__ data, const T* __restrict__ gout,
@@ -302,6 +373,17 @@ extern "C" int oc_dwconv_fwd(const void* data, int64_t n_in, const float* weight
   const int64_t work = n_out * (C / chunk_elems(dtype, vec));
   cudaStream_t s = (cudaStream_t)stream;
   const unsigned g = grid_1d(work, 256, 32);
+  if (vec && ((uintptr_t)weights % 16) == 0) {
+    bool done = false;
+    if (idx_bytes == 8)
+      OC_DISPATCH_T(dtype, (done = launch_dwconv_staged<T, int64_t>(data, weights, table, table_cols, taps, K, n_out, C, out, s)));
+    else
+      OC_DISPATCH_T(dtype, (done = launch_dwconv_staged<T, int32_t>(data, weights, table, table_cols, taps, K, n_out, C, out, s)));
+    if (done) {
+      OC_LAUNCH_OK("dwconv_staged_kernel");
+      return OC_OK;
+    }
+  }
   if (idx_bytes == 8)
     OC_DISPATCH_TV(dtype, vec, (dwconv_kernel<T, int64_t, V><<<g, 256, 0, s>>>((const T*)data, weights, (const int64_t*)table, table_cols, taps, K, n_out, C, (T*)out)));
   else

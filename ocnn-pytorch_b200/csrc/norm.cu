@@ -73,6 +73,124 @@ __global__ void colstats_final_kernel(const float* __restrict__ part_a, const fl
   if (sum_ab) sum_ab[c] = s2;
 }
 
+
+// ---- 16-byte vectorised variants (C a multiple of 16 / sizeof(T), aligned pointers) ----
+template <typename T> struct VecOf { static constexpr int N = 16 / sizeof(T); };
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* p, float (&v)[16 / sizeof(T)]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < (int)(16 / sizeof(T)); ++i) v[i] = to_f32<T>(e[i]);
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* p, const float (&v)[16 / sizeof(T)]) {
+  uint4 raw;
+  T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < (int)(16 / sizeof(T)); ++i) e[i] = from_f32<T>(v[i]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+// Thread (rl, v) sums the 16-byte vector v of the rows rl, rl + RL, ... of the block's
+// slice; row lanes are then folded through shared memory.  VPR = vectors per row.
+template <typename T>
+__global__ void __launch_bounds__(CS_THREADS)
+colstats_vec_kernel(const T* __restrict__ a, const T* __restrict__ b, int64_t n, int64_t rows_per_split, int C,
+                    float* __restrict__ part_a, float* __restrict__ part_ab) {
+  constexpr int N = 16 / sizeof(T);
+  extern __shared__ float sm[];                 // [2][RL][VW * N]
+  const int VPR = C / N;
+  const int VW = VPR < CS_THREADS ? VPR : CS_THREADS;   // vectors handled per pass
+  const int RL = CS_THREADS / VW;
+  const int v = threadIdx.x % VW, rl = threadIdx.x / VW;
+  const bool active = rl < RL;
+  const int64_t r0 = (int64_t)blockIdx.x * rows_per_split;
+  int64_t r1 = r0 + rows_per_split;
+  if (r1 > n) r1 = n;
+  for (int v0 = 0; v0 < VPR; v0 += VW) {
+    const int vv = v0 + v;
+    float s1[N], s2[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) { s1[i] = 0.f; s2[i] = 0.f; }
+    if (active && vv < VPR) {
+      for (int64_t r = r0 + rl; r < r1; r += RL) {
+        float x[N], y[N];
+        load_vec<T>(a + r * C + vv * N, x);
+        if (b) load_vec<T>(b + r * C + vv * N, y);
+#pragma unroll
+        for (int i = 0; i < N; ++i) { s1[i] += x[i]; s2[i] = fmaf(x[i], b ? y[i] : x[i], s2[i]); }
+      }
+    }
+    if (active) {
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        sm[(rl * VW + v) * N + i] = s1[i];
+        sm[(RL * VW + rl * VW + v) * N + i] = s2[i];
+      }
+    }
+    __syncthreads();
+    // fold the RL row lanes: one thread per channel of this pass
+    for (int c = threadIdx.x; c < VW * N; c += CS_THREADS) {
+      const int ch = v0 * N + c;
+      if (ch < C) {
+        float t1 = 0.f, t2 = 0.f;
+        for (int l = 0; l < RL; ++l) { t1 += sm[l * VW * N + c]; t2 += sm[(RL + l) * VW * N + c]; }
+        part_a[(int64_t)blockIdx.x * C + ch] = t1;
+        part_ab[(int64_t)blockIdx.x * C + ch] = t2;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T>
+__global__ void affine_cols_vec_kernel(const T* __restrict__ x, const float* __restrict__ scale,
+                                       const float* __restrict__ shift, int64_t nvec, int VPR, T* __restrict__ out) {
+  constexpr int N = 16 / sizeof(T);
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < nvec; t += (int64_t)gridDim.x * blockDim.x) {
+    const int c0 = (int)(t % VPR) * N;
+    float v[N];
+    load_vec<T>(x + t * N, v);
+#pragma unroll
+    for (int i = 0; i < N; ++i) v[i] = fmaf(v[i], scale[c0 + i], shift[c0 + i]);
+    store_vec<T>(out + t * N, v);
+  }
+}
+
+template <typename T>
+__global__ void bn_bwd_apply_vec_kernel(const T* __restrict__ g, const T* __restrict__ x, const float* __restrict__ ka,
+                                        const float* __restrict__ kb, const float* __restrict__ kc, int64_t nvec,
+                                        int VPR, T* __restrict__ gin) {
+  constexpr int N = 16 / sizeof(T);
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < nvec; t += (int64_t)gridDim.x * blockDim.x) {
+    const int c0 = (int)(t % VPR) * N;
+    float gv[N], xv[N];
+    load_vec<T>(g + t * N, gv);
+    load_vec<T>(x + t * N, xv);
+#pragma unroll
+    for (int i = 0; i < N; ++i) gv[i] = gv[i] * ka[c0 + i] + xv[i] * kb[c0 + i] + kc[c0 + i];
+    store_vec<T>(gin + t * N, gv);
+  }
+}
+
+static inline bool vec16_ok(int C, int dtype, const void* p0, const void* p1, const void* p2) {
+  const int N = (int)(16 / dtype_size(dtype));
+  return C % N == 0 && ((uintptr_t)p0 % 16) == 0 && ((uintptr_t)p1 % 16) == 0 && ((uintptr_t)p2 % 16) == 0;
+}
+
+template <typename T>
+static void launch_colstats_vec(const void* a, const void* b, int64_t n, int C, int splits, int64_t rps, float* pa,
+                                float* pab, cudaStream_t s) {
+  constexpr int N = 16 / sizeof(T);
+  const int VPR = C / N;
+  const int VW = VPR < CS_THREADS ? VPR : CS_THREADS;
+  const int RL = CS_THREADS / VW;
+  const size_t smem = (size_t)2 * RL * VW * N * sizeof(float);
+  colstats_vec_kernel<T><<<splits, CS_THREADS, smem, s>>>((const T*)a, (const T*)b, n, rps, C, pa, pab);
+}
+
 size_t colstats_workspace_bytes(int64_t n, int C) {
   return align_up((size_t)cs_splits(n) * C * 2 * sizeof(float), 256);
 }
@@ -91,7 +209,11 @@ int launch_colstats(const void* a, const void* b, int64_t n, int C, int dtype, f
   float* pab = pa + (size_t)splits * C;
   const int64_t rps = cdiv(n, splits);
   const int CT = cs_ct(C);
-  if (dtype == OC_F32)
+  if (vec16_ok(C, dtype, a, b, nullptr) && C <= 8192) {
+    if (dtype == OC_F32) launch_colstats_vec<float>(a, b, n, C, splits, rps, pa, pab, s);
+    else if (dtype == OC_F16) launch_colstats_vec<__half>(a, b, n, C, splits, rps, pa, pab, s);
+    else launch_colstats_vec<__nv_bfloat16>(a, b, n, C, splits, rps, pa, pab, s);
+  } else if (dtype == OC_F32)
     colstats_kernel<float><<<splits, CS_THREADS, 0, s>>>((const float*)a, (const float*)b, 0, n, rps, C, CT, pa, pab);
   else if (dtype == OC_F16)
     colstats_kernel<__half><<<splits, CS_THREADS, 0, s>>>((const __half*)a, (const __half*)b, 0, n, rps, C, CT, pa, pab);
@@ -413,6 +535,14 @@ extern "C" int oc_affine_cols(const void* x, const float* scale, const float* sh
   cudaStream_t s = (cudaStream_t)stream;
   const int64_t total = n * C;
   const unsigned g = grid_1d(total, 256, 32);
+  if (vec16_ok(C, dtype, x, out, nullptr)) {
+    const int N = (int)(16 / dtype_size(dtype));
+    const int64_t nvec = total / N;
+    const unsigned gv = grid_1d(nvec, 256, 32);
+    if (dtype == OC_F32) affine_cols_vec_kernel<float><<<gv, 256, 0, s>>>((const float*)x, scale, shift, nvec, C / N, (float*)out);
+    else if (dtype == OC_F16) affine_cols_vec_kernel<__half><<<gv, 256, 0, s>>>((const __half*)x, scale, shift, nvec, C / N, (__half*)out);
+    else affine_cols_vec_kernel<__nv_bfloat16><<<gv, 256, 0, s>>>((const __nv_bfloat16*)x, scale, shift, nvec, C / N, (__nv_bfloat16*)out);
+  } else
   if (dtype == OC_F32) affine_cols_kernel<float><<<g, 256, 0, s>>>((const float*)x, scale, shift, total, C, (float*)out);
   else if (dtype == OC_F16) affine_cols_kernel<__half><<<g, 256, 0, s>>>((const __half*)x, scale, shift, total, C, (__half*)out);
   else affine_cols_kernel<__nv_bfloat16><<<g, 256, 0, s>>>((const __nv_bfloat16*)x, scale, shift, total, C, (__nv_bfloat16*)out);
@@ -429,6 +559,14 @@ extern "C" int oc_bn_bwd_apply(const void* g, const void* x, const float* ka, co
   cudaStream_t s = (cudaStream_t)stream;
   const int64_t total = n * C;
   const unsigned gr = grid_1d(total, 256, 32);
+  if (vec16_ok(C, dtype, g, x, grad_in)) {
+    const int N = (int)(16 / dtype_size(dtype));
+    const int64_t nvec = total / N;
+    const unsigned gv = grid_1d(nvec, 256, 32);
+    if (dtype == OC_F32) bn_bwd_apply_vec_kernel<float><<<gv, 256, 0, s>>>((const float*)g, (const float*)x, ka, kb, kc, nvec, C / N, (float*)grad_in);
+    else if (dtype == OC_F16) bn_bwd_apply_vec_kernel<__half><<<gv, 256, 0, s>>>((const __half*)g, (const __half*)x, ka, kb, kc, nvec, C / N, (__half*)grad_in);
+    else bn_bwd_apply_vec_kernel<__nv_bfloat16><<<gv, 256, 0, s>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)x, ka, kb, kc, nvec, C / N, (__nv_bfloat16*)grad_in);
+  } else
   if (dtype == OC_F32) bn_bwd_apply_kernel<float><<<gr, 256, 0, s>>>((const float*)g, (const float*)x, ka, kb, kc, total, C, (float*)grad_in);
   else if (dtype == OC_F16) bn_bwd_apply_kernel<__half><<<gr, 256, 0, s>>>((const __half*)g, (const __half*)x, ka, kb, kc, total, C, (__half*)grad_in);
   else bn_bwd_apply_kernel<__nv_bfloat16><<<gr, 256, 0, s>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)x, ka, kb, kc, total, C, (__nv_bfloat16*)grad_in);
