@@ -63,7 +63,7 @@ class ClockSampler:
          'clocks_event_reasons.sw_power_cap')
     try:
       self.proc = subprocess.Popen(['nvidia-smi', '-i', str(self.index), '--query-gpu=' + q,
-                                    '--format=csv,noheader,nounits', '-lms', '100'],
+                                    '--format=csv,noheader,nounits', '-lms', '50'],
                                    stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
       self.thread = threading.Thread(target=self._read, daemon=True)
       self.thread.start()
@@ -309,7 +309,7 @@ def run_ours(args):
       'ms_fwd_kernel': ms_fwd, 'build': {'mpts_per_s': build_mpts, 'points': BATCH * NPTS,
                                          'what': 'pinned host points -> octree + neighbour tables, depth 8'},
       'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': pk['tflops'], 'unit': 'TFLOP/s',
-                   'frac': achieved / pk['tflops'], 'traffic': None,
+                   'frac': achieved / pk['tflops'], 'traffic': 448.0 * n,
                    'kernel': 'conv gather implicit GEMM (forward launch), valid-tap FLOPs', 'peak_src': pk['src']},
       'e2e': {'value': world * flops_valid / (ms_e2e * 1e-3) / 1e12, 'unit': UNIT,
               'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h, 'ms_per_step': ms_e2e},
