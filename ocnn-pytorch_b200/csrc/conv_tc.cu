@@ -9,7 +9,7 @@
 //
 // One persistent CTA per SM walks 128-row output tiles.  Warp roles:
 //   warps 0-3  epilogue : TMEM -> registers -> (+bias, cast) -> global
-//   warps 4-11 producers: prefetch the tile's neighbour indices and publish them in
+//   warps 5-7, 9-11, 13-14 producers: prefetch the tile's neighbour indices and publish them in
 //                         shared memory, then issue the stages; stage = (tap,
 //                         64-channel block).  A operand: the 128 gathered input rows,
 //                         copied by cp.async (16 B per lane, 8 lanes per row,
@@ -19,7 +19,7 @@
 //                         B operand: the matching block of the pre-swizzled weight
 //                         image, one bulk copy.  Taps with no valid neighbour in
 //                         the whole tile are skipped (warp-OR of the index signs).
-//   warp 12    MMA issuer: tcgen05.mma 128 x Cout x 16 per K step, accumulators
+//   warp 4     MMA issuer: tcgen05.mma 128 x Cout x 16 per K step, accumulators
 //                         double-buffered in TMEM so the epilogue of tile i
 //                         overlaps the main loop of tile i+1.
 // Stages flow through a ring of full/empty mbarriers; a per-stage header tells
@@ -40,8 +40,13 @@ constexpr int A_BYTES = TILE_M * 128;    // 16 KB
 constexpr int PROD_WARPS = 8;             // warps 4..11 gather; warp 12 issues the MMAs
 constexpr int PROD_THREADS = PROD_WARPS * 32;
 constexpr int FSPLIT = PROD_THREADS / TILE_M;    // threads that share the index prefetch of one row
-constexpr int MMA_WARP = 4 + PROD_WARPS;
-constexpr int THREADS = (MMA_WARP + 1) * 32;
+// Warp roles by index: 0-3 epilogue, 4 MMA issuer, producers = the warps > 4 whose index is
+// not a multiple of 4.  The MMA warp then shares its SM sub-partition (warp % 4 == 0) with no
+// producer: tcgen05.mma and cp.async leave through the same per-partition memory-instruction
+// queue, and behind a producer's slowly draining cp.async an MMA took ~3x longer to issue.
+constexpr int MMA_WARP = 4;
+constexpr int N_WARPS = 5 + PROD_WARPS + (PROD_WARPS + 2) / 3;   // producers plus the skipped multiples of 4
+constexpr int THREADS = N_WARPS * 32;
 constexpr int MAX_STAGES = 8;
 constexpr int MAX_NT = 256;
 
@@ -151,10 +156,11 @@ conv_tc_kernel(const Params p) {
   tc_fence_after();
   const uint32_t tmem_base = misc[0];
 
-  if (warp >= 4 && warp < MMA_WARP) {
+  const int pw_raw = (warp - 5) - ((warp - 5) >> 2);     // producer number of warps 5,6,7,9,10,11,13,14,...
+  if (warp > 4 && (warp & 3) != 0 && pw_raw < PROD_WARPS) {
     // ===================================================================== producers
-    const int pt = threadIdx.x - 128;          // 0..255
-    const int pw = warp - 4;
+    const int pw = pw_raw;
+    const int pt = pw * 32 + lane;             // 0..255
     const int frow = pt & (TILE_M - 1);        // index prefetch: row `frow`, taps k = fpart (mod FSPLIT)
     const int fpart = pt >> 7;
     const I* table = (const I*)p.table;
@@ -302,7 +308,7 @@ conv_tc_kernel(const Params p) {
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp < 4) {
     // ===================================================================== epilogue (warps 0-3)
     uint32_t acc = 0, acc_phase[2] = {0, 0};
     const bool has_bias = p.bias != nullptr;

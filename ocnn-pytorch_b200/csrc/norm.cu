@@ -377,6 +377,111 @@ __global__ void gn_bwd_apply_kernel(const T* __restrict__ g, const T* __restrict
   }
 }
 
+
+// 16-byte vectorised GroupNorm kernels (same arithmetic as the scalar ones above).
+template <typename T, int MODE>
+__global__ void __launch_bounds__(CS_THREADS)
+gn_partial_vec_kernel(const T* __restrict__ x, const T* __restrict__ g, GnOffsets offs, int b0, int C, int cpg,
+                      const float* __restrict__ mean, const float* __restrict__ inv_std,
+                      const float* __restrict__ weight, float* __restrict__ p1, float* __restrict__ p2) {
+  constexpr int N = 16 / sizeof(T);
+  extern __shared__ float sm[];                 // [2][RL][VW * N]
+  const int bl = blockIdx.y;
+  const int b = b0 + bl;
+  const int G = C / cpg;
+  const int64_t rb = offs.o[bl], re = offs.o[bl + 1];
+  const int64_t rps = (re - rb + GN_SPLITS - 1) / GN_SPLITS;
+  const int64_t r0 = rb + (int64_t)blockIdx.x * rps;
+  int64_t r1 = r0 + rps;
+  if (r1 > re) r1 = re;
+  const int VPR = C / N;
+  const int VW = VPR < CS_THREADS ? VPR : CS_THREADS;
+  const int RL = CS_THREADS / VW;
+  const int v = threadIdx.x % VW, rl = threadIdx.x / VW;
+  const bool active = rl < RL;
+  for (int v0 = 0; v0 < VPR; v0 += VW) {
+    const int vv = v0 + v;
+    float s1[N], s2[N], m[N], is[N], w[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) { s1[i] = 0.f; s2[i] = 0.f; m[i] = 0.f; is[i] = 0.f; w[i] = 0.f; }
+    if (active && vv < VPR) {
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        const int c = vv * N + i;
+        if (MODE >= 1) m[i] = mean[b * G + c / cpg];
+        if (MODE == 3) is[i] = inv_std[b * G + c / cpg];
+        if (MODE == 2) w[i] = weight[c];
+      }
+      for (int64_t r = r0 + rl; r < r1; r += RL) {
+        float xv[N], gv[N];
+        load_vec<T>(x + r * C + vv * N, xv);
+        if (MODE >= 2) load_vec<T>(g + r * C + vv * N, gv);
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          if (MODE == 0) s1[i] += xv[i];
+          if (MODE == 1) { const float d = xv[i] - m[i]; s1[i] = fmaf(d, d, s1[i]); }
+          if (MODE == 2) { const float gw = gv[i] * w[i]; s1[i] += gw; s2[i] = fmaf(gw, xv[i] - m[i], s2[i]); }
+          if (MODE == 3) { s1[i] += gv[i]; s2[i] = fmaf(gv[i], (xv[i] - m[i]) * is[i], s2[i]); }
+        }
+      }
+    }
+    if (active) {
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        sm[(rl * VW + v) * N + i] = s1[i];
+        sm[(RL * VW + rl * VW + v) * N + i] = s2[i];
+      }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < VW * N; c += CS_THREADS) {
+      const int ch = v0 * N + c;
+      if (ch < C) {
+        float t1 = 0.f, t2 = 0.f;
+        for (int l = 0; l < RL; ++l) { t1 += sm[l * VW * N + c]; t2 += sm[(RL + l) * VW * N + c]; }
+        const int64_t o = ((int64_t)b * GN_SPLITS + blockIdx.x) * C + ch;
+        p1[o] = t1;
+        if (p2) p2[o] = t2;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// MODE 0: out = (x - mean) * inv_std * weight + bias ; MODE 1: grad_in (see gn_bwd_apply_kernel)
+template <typename T, int MODE>
+__global__ void gn_apply_vec_kernel(const T* __restrict__ x, const T* __restrict__ g, GnOffsets offs, int b0, int nb,
+                                    int C, int cpg, const float* __restrict__ mean, const float* __restrict__ inv_std,
+                                    const float* __restrict__ weight, const float* __restrict__ bias,
+                                    const float* __restrict__ coef_a, const float* __restrict__ coef_b,
+                                    T* __restrict__ out) {
+  constexpr int N = 16 / sizeof(T);
+  const int G = C / cpg;
+  const int VPR = C / N;
+  const int64_t rb = offs.o[0], re = offs.o[nb];
+  for (int64_t t = rb * VPR + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < re * VPR;
+       t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = t / VPR;
+    const int c0 = (int)(t - r * VPR) * N;
+    int lo = 0, hi = nb - 1;                    // octree of row r: offs.o[lo] <= r < offs.o[lo + 1]
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (r >= offs.o[mid]) lo = mid; else hi = mid - 1;
+    }
+    float xv[N], gv[N], o[N];
+    load_vec<T>(x + t * N, xv);
+    if (MODE == 1) load_vec<T>(g + t * N, gv);
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const int c = c0 + i;
+      const int gi = (b0 + lo) * G + c / cpg;
+      const float y = xv[i] - mean[gi];
+      if (MODE == 0) o[i] = y * inv_std[gi] * weight[c] + bias[c];
+      else o[i] = gv[i] * weight[c] * inv_std[gi] + y * coef_a[gi] + coef_b[gi];
+    }
+    store_vec<T>(out + t * N, o);
+  }
+}
+
 // grad_weight[c] = sum_b sum_splits p2, grad_bias[c] = ... p1 (MODE 3 partials)
 __global__ void gn_param_grad_kernel(const float* __restrict__ p1, const float* __restrict__ p2,
                                      int batch, int C, float* __restrict__ gw, float* __restrict__ gb) {
@@ -418,6 +523,14 @@ static void gn_partials(const void* x, const void* g, const int64_t* h_offsets, 
     GnOffsets o;
     for (int i = 0; i <= nb; ++i) o.o[i] = h_offsets[b0 + i];
     dim3 grid(GN_SPLITS, nb);
+    constexpr int N = 16 / sizeof(T);
+    if (C % N == 0 && C <= 8192 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)g % 16) == 0) {
+      const int VPR = C / N;
+      const int VW = VPR < CS_THREADS ? VPR : CS_THREADS;
+      const size_t smem = (size_t)2 * (CS_THREADS / VW) * VW * N * sizeof(float);
+      gn_partial_vec_kernel<T, MODE><<<grid, CS_THREADS, smem, s>>>((const T*)x, (const T*)g, o, b0, C, cpg, mean,
+                                                                    inv_std, weight, p1, p2);
+    } else
     gn_partial_kernel<T, MODE><<<grid, CS_THREADS, 0, s>>>((const T*)x, (const T*)g, o, b0, C, cpg, CT, mean,
                                                            inv_std, weight, p1, p2);
   }
@@ -619,6 +732,10 @@ extern "C" int oc_gn_fwd(const void* x, const int64_t* h_offsets, int batch, int
     for (int i = 0; i <= nb; ++i) o.o[i] = h_offsets[b0 + i];
     const int64_t total = (o.o[nb] - o.o[0]) * C;
     if (total == 0) continue;
+    if (vec16_ok(C, dtype, x, out, nullptr)) {
+      const int N = (int)(16 / dtype_size(dtype));
+      GN_T(dtype, (gn_apply_vec_kernel<T, 0><<<grid_1d(total / N, 256, 32), 256, 0, s>>>((const T*)x, nullptr, o, b0, nb, C, cpg, mean, inv_std, weight, bias, nullptr, nullptr, (T*)out)));
+    } else
     GN_T(dtype, (gn_apply_kernel<T><<<grid_1d(total, 256, 32), 256, 0, s>>>((const T*)x, o, b0, nb, C, cpg, mean, inv_std, weight, bias, (T*)out)));
   }
   OC_LAUNCH_OK("group norm forward kernels");
@@ -652,6 +769,10 @@ extern "C" int oc_gn_bwd(const void* grad_out, const void* x, const int64_t* h_o
       for (int i = 0; i <= nb; ++i) o.o[i] = h_offsets[b0 + i];
       const int64_t total = (o.o[nb] - o.o[0]) * C;
       if (total == 0) continue;
+      if (vec16_ok(C, dtype, x, grad_out, grad_in)) {
+        const int N = (int)(16 / dtype_size(dtype));
+        GN_T(dtype, (gn_apply_vec_kernel<T, 1><<<grid_1d(total / N, 256, 32), 256, 0, s>>>((const T*)x, (const T*)grad_out, o, b0, nb, C, cpg, mean, inv_std, weight, nullptr, P.coef_a, P.coef_b, (T*)grad_in)));
+      } else
       GN_T(dtype, (gn_bwd_apply_kernel<T><<<grid_1d(total, 256, 32), 256, 0, s>>>((const T*)grad_out, (const T*)x, o, b0, nb, C, cpg, mean, inv_std, weight, P.coef_a, P.coef_b, (T*)grad_in)));
     }
   }

@@ -32,8 +32,11 @@ constexpr int TILE_R = 128;               // rows (the MMA K extent) per tile
 constexpr int BLK_BYTES = TILE_R * 128;   // one 64-channel block of 128 rows
 constexpr int PROD_WARPS = 8;
 constexpr int PROD_THREADS = PROD_WARPS * 32;
-constexpr int MMA_WARP = 4 + PROD_WARPS;
-constexpr int THREADS = (MMA_WARP + 1) * 32;
+// Warps 0-3: no main-loop role (epilogue at the end); warp 4: MMA issuer; producers: warps > 4
+// whose index is not a multiple of 4, so that the MMA warp's SM sub-partition holds no producer.
+constexpr int MMA_WARP = 4;
+constexpr int N_WARPS = 5 + PROD_WARPS + (PROD_WARPS + 2) / 3;
+constexpr int THREADS = N_WARPS * 32;
 constexpr int MAX_STAGES = 6;
 constexpr int MAX_MT = 16;                // M tiles (accumulators) per CTA
 
@@ -130,10 +133,11 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
   uint32_t group_taps = 0;
   for (int b = 2 * m_lo; b < 2 * (m_lo + m_cnt) && b < p.nblk; ++b) group_taps |= 1u << (b / p.KB);
 
-  if (warp >= 4 && warp < MMA_WARP) {
+  const int pw_raw = (warp - 5) - ((warp - 5) >> 2);
+  if (warp > 4 && (warp & 3) != 0 && pw_raw < PROD_WARPS) {
     // ===================================================================== producers
-    const int pt = threadIdx.x - 128;
-    const int pw = warp - 4;
+    const int pw = pw_raw;
+    const int pt = pw * 32 + lane;
     const int frow = pt & (TILE_R - 1);
     const int fhalf = pt >> 7;
     const I* table = (const I*)p.table;
