@@ -31,6 +31,23 @@
 namespace oc {
 
 __device__ int g_tc_status = 0;  // sticky: non-zero after any abandoned wait
+// Profiling build (-DOC_PROF): every role accumulates clock64() intervals (time waiting on
+// each barrier, time issuing copies / MMAs) and adds them to g_prof at exit; oc_debug_prof
+// reads the totals.  -DOC_NOCOPY drops the gather copies and -DOC_NOMMA the MMAs, which
+// shows how fast each side of the pipeline runs alone (results are then meaningless).
+// None of this is compiled into the shipped library.
+#ifdef OC_PROF
+__device__ unsigned long long g_prof[64];
+#define PROF_T(v) const long long v = clock64()
+#define PROF_ADD(i, d) pr[i] += (d)
+#define PROF_DECL long long pr[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define PROF_FLUSH(base, n) if (lane == 0) { for (int _i = 0; _i < (n); ++_i) atomicAdd(&g_prof[(base) + _i], (unsigned long long)pr[_i]); }
+#else
+#define PROF_T(v)
+#define PROF_ADD(i, d)
+#define PROF_DECL
+#define PROF_FLUSH(base, n)
+#endif
 
 namespace tc {
 
@@ -176,13 +193,15 @@ conv_tc_kernel(const Params p) {
     const int chunk = lane & 7;
     const int grp = lane >> 3;
     const int n_own = S < PROD_WARPS ? S : PROD_WARPS;   // warps that own stages (a warp needs a slot of its own)
-    uint32_t gstage = 0;                       // running stage number of this CTA (same in every warp)
+    int owner = 0;                             // producer warp that owns the next stage
     int s = 0;                                 // ring slot of the next stage
     uint32_t ring_phase = 0;                   // flips each time the ring wraps
     constexpr int NF = (OC_MAX_TAPS + FSPLIT - 1) / FSPLIT;
     int nidx[NF];
     bool ok = true;
     uint32_t psync_phase = 0;
+    PROF_DECL;
+    PROF_T(p_start);
 
     auto fetch_indices = [&](int64_t tile) {
       const int64_t r = tile * TILE_M + frow;
@@ -224,26 +243,35 @@ conv_tc_kernel(const Params p) {
     }
     for (; tile < n_tiles && ok; tile += gridDim.x) {
       const int64_t next = tile + gridDim.x;
+      PROF_T(pf0);
       if (next < n_tiles) fetch_indices(next);   // loads stay in flight during this tile
+      PROF_T(pf1); PROF_ADD(3, pf1 - pf0);
       if (mask == 0) mask = 1;                   // nothing valid: one all-zero stage keeps the flow uniform
       const int* cur = sidx + buf * (OC_MAX_TAPS * TILE_M);
+      PROF_T(pl0);
       const uint32_t last_k = 31 - __clz(mask);
       const uint32_t first_k = __ffs(mask) - 1;
       for (uint32_t k = first_k; k <= last_k && ok; ++k) {
         if (!((mask >> k) & 1u)) continue;
         for (int kb = 0; kb < p.KB; ++kb) {
-          const bool mine = (int)(gstage % (uint32_t)n_own) == pw;
-          ++gstage;
+          const bool mine = owner == pw;            // stages are dealt round-robin
+          if (++owner == n_own) owner = 0;
           if (mine) {
+            PROF_T(pw0);
             if (!mbar_wait(empty_bar(s), ring_phase ^ 1u, abort_flag, &g_tc_status, 1)) { ok = false; break; }
+            PROF_T(pw1); PROF_ADD(0, pw1 - pw0);
             const uint32_t a_dst = s_base + L.ring + s * L.stage_bytes;
             const int kc = min(KBLK, p.Cin - kb * KBLK);          // channels in this block
             if (lane == 0) {
-              hdr[s] = (k == first_k && kb == 0 ? 1u : 0u) | (k == last_k && kb == p.KB - 1 ? 2u : 0u) |
-                       ((uint32_t)(kc / 16) << 8);
+              if (k == first_k && kb == 0) hdr[s] = (uint32_t)__popc(mask) * (uint32_t)p.KB;   // stages of this tile
+#ifdef OC_NOCOPY
+              mbar_arrive(full_bar(s));
+#else
               mbar_arrive_expect_tx(full_bar(s), b_bytes);
               bulk_g2s(a_dst + A_BYTES, wimg + ((size_t)k * p.KB + kb) * b_bytes, b_bytes, full_bar(s));
+#endif
             }
+#ifndef OC_NOCOPY
             if (chunk * 8 < kc) {
               const uint8_t* lane_src = data + (size_t)kb * 128 + chunk * 16;
               const int* irow = cur + k * TILE_M + grp * 32;
@@ -260,62 +288,103 @@ conv_tc_kernel(const Params p) {
                 }
               }
             }
+#endif
             // arrives on the stage's barrier once this lane's copies have landed; the lane
             // itself does not wait, so every warp keeps a whole stage in flight
             cp_async_arrive_noinc(full_bar(s));
+            PROF_T(pw2); PROF_ADD(1, pw2 - pw1); PROF_ADD(2, 1);
           }
           if (++s == S) { s = 0; ring_phase ^= 1u; }
         }
       }
+      PROF_T(pl1); PROF_ADD(6, pl1 - pl0);
       if (next < n_tiles) {
+        PROF_T(pp0);
         buf ^= 1;
         mask = publish_indices(buf);
+        PROF_T(pp1); PROF_ADD(4, pp1 - pp0);
       }
     }
+    PROF_T(p_end); PROF_ADD(5, p_end - p_start);
+    PROF_FLUSH(0, 7);
     cp_async_wait_all();   // nothing of this thread may still be writing shared memory at exit
   } else if (warp == MMA_WARP) {
     // ===================================================================== MMA issuer
-    if (lane == 0) {
+    // All 32 lanes run the loop (waits, header reads, address arithmetic) so that it is
+    // warp-uniform; one elected lane issues the tcgen05 instructions.
+    {
+      // Descriptors are formed incrementally: the low word of a descriptor holds the start
+      // address >> 4, so slot s / K step ks only add s * (stage_bytes / 16) + 2 * ks to the
+      // low word of the descriptor of slot 0.  Rebuilding the 64-bit descriptor from a
+      // run-time address for every MMA makes this loop about twice as slow.
       const uint32_t idesc = make_idesc(BF16 ? 1 : 0, 0, 0, TILE_M, p.NT);
+      const uint64_t da0 = make_desc_sw128(s_base + L.ring, 16, 1024);
+      const uint64_t db0 = make_desc_sw128(s_base + L.ring + A_BYTES, 16, 1024);
+      const uint64_t desc_hi = da0 & 0xffffffff00000000ull;
+      const uint32_t la0 = (uint32_t)da0, lb0 = (uint32_t)db0;
+      const uint32_t sb16 = L.stage_bytes >> 4;
+      const bool nk4 = (p.Cin & (KBLK - 1)) == 0;       // every K block is full: 4 MMAs per stage
       int s = 0;
-      uint32_t ring_phase = 0;
-      uint32_t acc = 0, acc_phase[2] = {0, 0};
+      uint32_t ring_phase = 0, acc = 0, acc_phase = 0;  // acc_phase: bit a = phase of accumulator a
       bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag, &g_tc_status, 2)) break;
+      PROF_DECL;
+      PROF_T(m_start);
+      for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        PROF_T(mt0);
+        ok = mbar_wait(tempty_bar(acc), ((acc_phase >> acc) & 1u) ^ 1u, abort_flag, &g_tc_status, 2);
+        if (__any_sync(0xffffffffu, !ok)) break;
         tc_fence_after();
+        PROF_T(mt1); PROF_ADD(0, mt1 - mt0);
         const uint32_t d_tmem = tmem_base + acc * (uint32_t)p.NT;
-        for (;;) {
-          if (!mbar_wait(full_bar(s), ring_phase, abort_flag, &g_tc_status, 3)) { ok = false; break; }
+        uint32_t n_st = 1;
+        int kb = 0;
+        for (uint32_t st = 0; st < n_st; ++st) {
+          PROF_T(mf0);
+          ok = mbar_wait(full_bar(s), ring_phase, abort_flag, &g_tc_status, 3);
+          if (__any_sync(0xffffffffu, !ok)) break;
           tc_fence_after();
-          const uint32_t h = hdr[s];
-          const uint32_t nk = h >> 8;
-          const uint32_t a_addr = s_base + L.ring + s * L.stage_bytes;
-          const uint32_t b_addr = a_addr + A_BYTES;
-          for (uint32_t ks = 0; ks < nk; ++ks) {
-            const uint64_t da = make_desc_sw128(a_addr + ks * 32, 16, 1024);
-            const uint64_t db = make_desc_sw128(b_addr + ks * 32, 16, 1024);
-            umma_f16(d_tmem, da, db, idesc, ((h & 1u) && ks == 0) ? 0u : 1u);
+          PROF_T(mf1); PROF_ADD(1, mf1 - mf0);
+          // the first stage of a tile carries the tile's stage count
+          if (st == 0) n_st = __reduce_or_sync(0xffffffffu, hdr[s]);
+          const uint32_t la = la0 + (uint32_t)s * sb16, lb = lb0 + (uint32_t)s * sb16;
+#ifndef OC_NOMMA
+          if (nk4) {
+#pragma unroll
+            for (uint32_t ks = 0; ks < 4; ++ks)
+              if (elect_one())
+                umma_f16(d_tmem, desc_hi | (la + 2 * ks), desc_hi | (lb + 2 * ks), idesc, (st == 0 && ks == 0) ? 0u : 1u);
+          } else {
+            const uint32_t nk = (uint32_t)min(KBLK, p.Cin - kb * KBLK) >> 4;
+            for (uint32_t ks = 0; ks < nk; ++ks)
+              if (elect_one())
+                umma_f16(d_tmem, desc_hi | (la + 2 * ks), desc_hi | (lb + 2 * ks), idesc, (st == 0 && ks == 0) ? 0u : 1u);
           }
-          umma_commit(empty_bar(s));         // stage reusable once these MMAs have read it
+#endif
+          if (elect_one()) umma_commit(empty_bar(s));         // slot reusable once these MMAs have read it
           if (++s == S) { s = 0; ring_phase ^= 1u; }
-          if (h & 2u) break;
+          if (++kb == p.KB) kb = 0;
+          PROF_T(mf2); PROF_ADD(2, mf2 - mf1); PROF_ADD(3, 1);
         }
         if (!ok) break;
-        umma_commit(tfull_bar(acc));         // accumulator complete
-        acc_phase[acc] ^= 1u;
+        if (elect_one()) umma_commit(tfull_bar(acc));         // accumulator complete
+        acc_phase ^= 1u << acc;
         acc ^= 1u;
       }
+      PROF_T(m_end); PROF_ADD(4, m_end - m_start);
+      PROF_FLUSH(8, 5);
     }
     __syncwarp();
   } else if (warp < 4) {
     // ===================================================================== epilogue (warps 0-3)
-    uint32_t acc = 0, acc_phase[2] = {0, 0};
+    uint32_t acc = 0, acc_phase = 0;
     const bool has_bias = p.bias != nullptr;
     uint16_t* out = (uint16_t*)p.out;
+    PROF_DECL;
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-      if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, &g_tc_status, 4, 256)) break;
+      PROF_T(e0);
+      if (!mbar_wait(tfull_bar(acc), (acc_phase >> acc) & 1u, abort_flag, &g_tc_status, 4, 256)) break;
       tc_fence_after();
+      PROF_T(e1); PROF_ADD(0, e1 - e0);
       const int64_t row = tile * TILE_M + warp * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + acc * (uint32_t)p.NT;
       for (int c0 = 0; c0 < p.NT; c0 += 16) {
@@ -335,9 +404,11 @@ conv_tc_kernel(const Params p) {
       }
       tc_fence_before();
       mbar_arrive(tempty_bar(acc));
-      acc_phase[acc] ^= 1u;
+      PROF_T(e2); PROF_ADD(1, e2 - e1); PROF_ADD(2, 1);
+      acc_phase ^= 1u << acc;
       acc ^= 1u;
     }
+    if (warp == 0) { PROF_FLUSH(16, 3); }
   }
 
   // ------------------------------------------------------------------------ teardown
@@ -486,4 +557,10 @@ int read_tc_status(cudaStream_t s, int* h_status) {
 
 }  // namespace oc
 
+#ifdef OC_PROF
+extern "C" int oc_debug_prof(unsigned long long* host64, int reset) {
+  if (reset) { unsigned long long z[64] = {0}; return (int)cudaMemcpyToSymbol(oc::g_prof, z, sizeof(z)); }
+  return (int)cudaMemcpyFromSymbol(host64, oc::g_prof, 64 * sizeof(unsigned long long));
+}
+#endif
 #include "wgrad_tc.cuh"

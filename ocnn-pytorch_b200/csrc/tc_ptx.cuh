@@ -152,6 +152,20 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// True in exactly one lane of a converged warp (always the same one).  The MMA-issuing
+// warp runs its loop with all 32 lanes and predicates only the tcgen05 instructions with
+// this: the loop state stays warp-uniform, so descriptors and addresses live in uniform
+// registers and an MMA issues in ~11 cycles instead of ~54 when a single diverged
+// thread runs the loop.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t.reg .b32 r;\n\t"
+      "elect.sync r|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
 // Arrives on `bar` when all MMAs issued so far by this thread have completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");

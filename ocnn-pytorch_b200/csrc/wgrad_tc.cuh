@@ -292,44 +292,47 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
     cp_async_wait_all();
   } else if (warp == MMA_WARP) {
     // ===================================================================== MMA issuer
-    if (lane == 0) {
+    // (all 32 lanes run the loop so that it stays warp-uniform; one elected lane issues)
+    {
       const uint32_t idesc = make_idesc(BF16 ? 1 : 0, 1, 1, 128, p.NTW);   // both operands MN-major
+      // MN-major, 128-byte swizzle: 64-element atoms along M / N are BLK_BYTES apart (leading
+      // offset), groups of 8 rows along K are 1024 B apart (stride offset).  Descriptors are
+      // formed by adding (offset >> 4) to the low word of the descriptor of slot 0, which
+      // issues about twice as fast as rebuilding them from a run-time address.
+      const uint64_t da0 = make_desc_sw128(s_base + L.ring, BLK_BYTES, 1024);
+      const uint64_t dg0 = make_desc_sw128(s_base + L.gbuf, BLK_BYTES, 1024);
+      const uint64_t desc_hi = da0 & 0xffffffff00000000ull;
+      const uint32_t la0 = (uint32_t)da0, lg0 = (uint32_t)dg0;
+      const uint32_t a_step = (uint32_t)(2 * BLK_BYTES) >> 4, g_step = (uint32_t)(p.GB * BLK_BYTES) >> 4;
       int s = 0;
       uint32_t ring_phase = 0;
-      uint32_t gb_sel = 0, g_phase[2] = {0, 0};
-      bool issued_any = false;
+      uint32_t gb_sel = 0, g_phase = 0;   // g_phase: bit b = phase of grad_out buffer b
       for (;;) {
         if (!mbar_wait(full_bar(s), ring_phase, abort_flag, &g_tc_status, 16)) break;
         tc_fence_after();
         const uint32_t h = hdr[s];
         if (h & 4u) break;
         if (h & 1u) {   // first stage of a row tile: its grad_out block must have landed
-          if (!mbar_wait(gfull_bar(gb_sel), g_phase[gb_sel], abort_flag, &g_tc_status, 17)) break;
+          if (!mbar_wait(gfull_bar(gb_sel), (g_phase >> gb_sel) & 1u, abort_flag, &g_tc_status, 17)) break;
           tc_fence_after();
         }
         const uint32_t m = h >> 8;
-        const uint32_t a_addr = s_base + L.ring + s * (uint32_t)(2 * BLK_BYTES);
-        const uint32_t g_addr = s_base + L.gbuf + gb_sel * (uint32_t)(p.GB * BLK_BYTES);
+        const uint32_t la = la0 + (uint32_t)s * a_step, lg = lg0 + gb_sel * g_step;
         const uint32_t d_tmem = tmem_base + m * (uint32_t)p.NTW;
 #pragma unroll
-        for (uint32_t ks = 0; ks < TILE_R / 16; ++ks) {
-          // MN-major, 128-byte swizzle: 64-element atoms along M / N are BLK_BYTES apart
-          // (leading offset), groups of 8 rows along K are 1024 B apart (stride offset)
-          const uint64_t da = make_desc_sw128(a_addr + ks * 2048, BLK_BYTES, 1024);
-          const uint64_t db = make_desc_sw128(g_addr + ks * 2048, BLK_BYTES, 1024);
-          umma_f16(d_tmem, da, db, idesc, ((h & 8u) && ks == 0) ? 0u : 1u);
-        }
-        issued_any = true;
-        umma_commit(empty_bar(s));
+        for (uint32_t ks = 0; ks < TILE_R / 16; ++ks)
+          if (elect_one())
+            umma_f16(d_tmem, desc_hi | (la + ks * 128), desc_hi | (lg + ks * 128), idesc, ((h & 8u) && ks == 0) ? 0u : 1u);
+        if (elect_one()) umma_commit(empty_bar(s));
         if (h & 2u) {   // last stage of the row tile: release the grad_out buffer
-          umma_commit(gempty_bar(gb_sel));
-          g_phase[gb_sel] ^= 1u;
+          if (elect_one()) umma_commit(gempty_bar(gb_sel));
+          g_phase ^= 1u << gb_sel;
           gb_sel ^= 1u;
         }
         if (++s == S) { s = 0; ring_phase ^= 1u; }
       }
-      (void)issued_any;
-      umma_commit(done_bar);
+      __syncwarp();
+      if (elect_one()) umma_commit(done_bar);
       mbar_wait(done_bar, 0, abort_flag, &g_tc_status, 18);   // all MMAs retired
     }
     __syncwarp();
