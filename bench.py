@@ -250,15 +250,16 @@ def run_ours(args):
 
   # ---- dominant kernel alone: the gather implicit GEMM (forward launch)
   table, taps = octree.conv_table(DEPTH, '333', 1, False)
+  tiles = octree.conv_tiles(DEPTH, '333', 1, False)
   xd = x.detach()
   reps = max(args.steps, 5)
   for _ in range(3):
-    b200.nn.conv_gather(xd, conv.weights, False, None, table, taps, CH, CH)
+    b200.nn.conv_gather(xd, conv.weights, False, None, table, taps, CH, CH, tiles)
   torch.cuda.synchronize()
   k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
   k0.record()
   for _ in range(reps):
-    b200.nn.conv_gather(xd, conv.weights, False, None, table, taps, CH, CH)
+    b200.nn.conv_gather(xd, conv.weights, False, None, table, taps, CH, CH, tiles)
   k1.record()
   torch.cuda.synchronize()
   ms_fwd = k0.elapsed_time(k1) / reps
@@ -355,10 +356,11 @@ def run_conv_only(args, b200, octree, dev):
   # the three launches of a step, timed one by one
   table, taps = octree.conv_table(DEPTH, '333', 1, False)
   table_t, taps_t = octree.conv_table_transposed(DEPTH, '333', 1, False)
+  tiles, tiles_t = octree.conv_tiles(DEPTH, '333', 1, False), octree.conv_tiles(DEPTH, '333', 1, False, True)
   xd = x.detach()
   parts = {}
-  for name, fn in (('fwd', lambda: b200.nn.conv_gather(xd, conv.weights, False, None, table, taps, CH, CH)),
-                   ('dgrad', lambda: b200.nn.conv_gather(gy, conv.weights, True, None, table_t, taps_t, CH, CH)),
+  for name, fn in (('fwd', lambda: b200.nn.conv_gather(xd, conv.weights, False, None, table, taps, CH, CH, tiles)),
+                   ('dgrad', lambda: b200.nn.conv_gather(gy, conv.weights, True, None, table_t, taps_t, CH, CH, tiles_t)),
                    ('wgrad', lambda: b200.nn.conv_wgrad(xd, gy, table, taps, CH, CH))):
     fn()
     torch.cuda.synchronize()
@@ -421,8 +423,9 @@ def run_suite(args, b200, octree, dev):
         w = (torch.randn(27, C, C, device=dev, generator=g) / (27 * C) ** 0.5)
         fl = 2.0 * nnz * C * C
         tag = dict(C=C, dtype=str(dtype).split('.')[-1], nempty=nempty, rows=n, valid_taps=nnz)
-        emit('conv333_fwd', _time(lambda: b200.nn.conv_gather(x, w, False, None, table, taps, C, C)), flops=fl, **tag)
-        emit('conv333_dgrad', _time(lambda: b200.nn.conv_gather(gy, w, True, None, table_t, taps_t, C, C)), flops=fl, **tag)
+        tl, tl_t = octree.conv_tiles(D, '333', 1, nempty), octree.conv_tiles(D, '333', 1, nempty, True)
+        emit('conv333_fwd', _time(lambda: b200.nn.conv_gather(x, w, False, None, table, taps, C, C, tl)), flops=fl, **tag)
+        emit('conv333_dgrad', _time(lambda: b200.nn.conv_gather(gy, w, True, None, table_t, taps_t, C, C, tl_t)), flops=fl, **tag)
         emit('conv333_wgrad', _time(lambda: b200.nn.conv_wgrad(x, gy, table, taps, C, C)), flops=fl, **tag)
         del x, gy
   # strided / transposed path (bf16), depth-wise conv, pooling, upsampling, normalisation

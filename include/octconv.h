@@ -160,6 +160,27 @@ int oc_conv_fwd(const void* data, int64_t n_in, const void* weights, int w_dtype
                 int table_cols, const int* h_taps, int K, int64_t n_out, int Cin, int Cout,
                 int dtype, void* out, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Tile table: the neighbour table of one convolution (the (n_out, table_cols) table that
+ * Octree.get_neigh returns, ocnn/octree/octree.py:490-523, restricted to `taps`) regrouped
+ * for the tensor-core kernel, which then fetches the indices of 128 output rows with one
+ * bulk copy instead of 27 strided loads per row.  Block t covers rows 128 t .. 128 t + 127:
+ * a 16-byte header (word 0 = bit mask of the taps that have an entry >= 0 in the block)
+ * followed by K rows of 128 int32, row k = column taps[k] (-1 = none, also past n_out).
+ * Build it once per (depth, kernel, stride, nempty) and reuse it for every layer and
+ * step on that octree level, like the reference caches `neigh`.  The reference has no
+ * counterpart; it is optional: oc_conv_fwd with the plain table gives the same result.
+ * oc_conv_tiled_supported: 1 where oc_conv_fwd_tiled accepts the shape (fp16 / bf16,
+ * Cin and Cout multiples of 16). */
+int oc_conv_tiled_supported(int K, int Cin, int Cout, int dtype);
+size_t oc_tile_table_bytes(int64_t n_out, int K);
+int oc_tile_table_build(const void* table, int idx_bytes, int table_cols, const int* h_taps, int K,
+                        int64_t n_out, void* tiles, size_t tiles_bytes, void* stream);
+/* oc_conv_fwd with the table given as a tile table (same K and tap order as at build). */
+int oc_conv_fwd_tiled(const void* data, int64_t n_in, const void* weights, int w_dtype,
+                      int w_transposed, const void* bias, const void* tiles, int K, int64_t n_out,
+                      int Cin, int Cout, int dtype, void* out, void* workspace,
+                      size_t workspace_bytes, void* stream);
+
 /* Weight gradient, ocnn/nn/octree_conv.py:170-202 (weight_gemm) and
  * kernels/conv_bwd_implicit_gemm_splitk.py:246-306:
  *   grad_w[k, ci, co] = sum_r data[table[r, taps[k]], ci] * grad_out[r, co]

@@ -98,25 +98,31 @@ extern "C" size_t oc_conv_workspace_bytes(int K, int Cin, int Cout, int dtype) {
   return conv_plan(K, Cin, Cout, dtype).total;
 }
 
-extern "C" int oc_conv_fwd(const void* data, int64_t n_in, const void* weights, int w_dtype,
-                           int w_transposed, const void* bias, const void* table, int idx_bytes,
-                           int table_cols, const int* h_taps, int K, int64_t n_out, int Cin,
-                           int Cout, int dtype, void* out, void* workspace, size_t workspace_bytes,
-                           void* stream) {
-  int rc = check_conv_common("oc_conv_fwd", K, Cin, Cout, dtype, idx_bytes, table_cols, n_in, n_out);
+// `tiles` non-null: the table comes as a tile table (tensor-core shapes only).
+static int conv_fwd_impl(const char* who, const void* data, int64_t n_in, const void* weights, int w_dtype,
+                         int w_transposed, const void* bias, const void* table, int idx_bytes,
+                         int table_cols, const int* h_taps, const void* tiles, int K, int64_t n_out, int Cin,
+                         int Cout, int dtype, void* out, void* workspace, size_t workspace_bytes,
+                         void* stream) {
+  int rc = check_conv_common(who, K, Cin, Cout, dtype, idx_bytes, table_cols, n_in, n_out);
   if (rc) return rc;
-  OC_REQUIRE(w_dtype == OC_F32 || w_dtype == dtype, OC_EINVAL,
-             "oc_conv_fwd: weights must be fp32 or the data dtype");
+  OC_REQUIRE(w_dtype == OC_F32 || w_dtype == dtype, OC_EINVAL, "%s: weights must be fp32 or the data dtype", who);
   ConvArgs a;
-  rc = make_taps(h_taps, K, table_cols, &a.taps, "oc_conv_fwd");
-  if (rc) return rc;
+  if (tiles) {
+    for (int k = 0; k < K; ++k) a.taps.t[k] = k;   // the tile table already holds the chosen taps, in order
+  } else {
+    rc = make_taps(h_taps, K, table_cols, &a.taps, who);
+    if (rc) return rc;
+  }
   if (n_out == 0) return OC_OK;
-  OC_REQUIRE(weights && table && out && workspace, OC_EINVAL, "oc_conv_fwd: null pointer");
-  OC_REQUIRE(data || n_in == 0, OC_EINVAL, "oc_conv_fwd: null data");
+  OC_REQUIRE(weights && (table || tiles) && out && workspace, OC_EINVAL, "%s: null pointer", who);
+  OC_REQUIRE(data || n_in == 0, OC_EINVAL, "%s: null data", who);
   const ConvPlan P = conv_plan(K, Cin, Cout, dtype);
-  OC_REQUIRE(workspace_bytes >= P.total, OC_ENOMEM, "oc_conv_fwd: workspace %zu < %zu bytes",
-             workspace_bytes, P.total);
-  a.data = data; a.n_in = n_in; a.bias = bias; a.table = table; a.idx_bytes = idx_bytes;
+  OC_REQUIRE(P.tc || !tiles, OC_EINVAL,
+             "%s: a tile table needs fp16/bf16 data and channel counts that are multiples of 16 "
+             "(ask oc_conv_tiled_supported); use oc_conv_fwd with the plain table", who);
+  OC_REQUIRE(workspace_bytes >= P.total, OC_ENOMEM, "%s: workspace %zu < %zu bytes", who, workspace_bytes, P.total);
+  a.data = data; a.n_in = n_in; a.bias = bias; a.table = table; a.tiled = tiles; a.idx_bytes = idx_bytes;
   a.table_cols = table_cols; a.K = K; a.n_out = n_out; a.Cin = Cin; a.Cout = Cout; a.dtype = dtype;
   a.out = out;
   cudaStream_t s = (cudaStream_t)stream;
@@ -129,6 +135,53 @@ extern "C" int oc_conv_fwd(const void* data, int64_t n_in, const void* weights, 
   rc = prep_weights_f32(weights, w_dtype, K, Cin, Cout, w_transposed, (float*)(ws + P.w_off), s);
   if (rc) return rc;
   return launch_conv_fma(a, (const float*)(ws + P.w_off), s);
+}
+
+extern "C" int oc_conv_fwd(const void* data, int64_t n_in, const void* weights, int w_dtype,
+                           int w_transposed, const void* bias, const void* table, int idx_bytes,
+                           int table_cols, const int* h_taps, int K, int64_t n_out, int Cin,
+                           int Cout, int dtype, void* out, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+  return conv_fwd_impl("oc_conv_fwd", data, n_in, weights, w_dtype, w_transposed, bias, table, idx_bytes,
+                       table_cols, h_taps, nullptr, K, n_out, Cin, Cout, dtype, out, workspace,
+                       workspace_bytes, stream);
+}
+
+extern "C" int oc_conv_tiled_supported(int K, int Cin, int Cout, int dtype) {
+  return (K >= 1 && K <= OC_MAX_TAPS && conv_tc_supported(K, Cin, Cout, dtype)) ? 1 : 0;
+}
+
+extern "C" size_t oc_tile_table_bytes(int64_t n_out, int K) {
+  if (K < 1 || K > OC_MAX_TAPS || n_out < 0) return 0;
+  return tile_table_bytes(n_out, K);
+}
+
+extern "C" int oc_tile_table_build(const void* table, int idx_bytes, int table_cols, const int* h_taps,
+                                   int K, int64_t n_out, void* tiles, size_t tiles_bytes, void* stream) {
+  OC_REQUIRE(K >= 1 && K <= OC_MAX_TAPS, OC_EINVAL, "oc_tile_table_build: K %d not in [1,27]", K);
+  OC_REQUIRE(idx_bytes == 8 || idx_bytes == 4, OC_EINVAL, "oc_tile_table_build: idx_bytes must be 4 or 8");
+  OC_REQUIRE(table_cols >= 1 && table_cols <= 27, OC_EINVAL, "oc_tile_table_build: table_cols %d not in [1,27]", table_cols);
+  OC_REQUIRE(n_out >= 0 && n_out < (1LL << 31), OC_EINVAL, "oc_tile_table_build: n_out must be in [0, 2^31)");
+  TapList taps;
+  int rc = make_taps(h_taps, K, table_cols, &taps, "oc_tile_table_build");
+  if (rc) return rc;
+  if (n_out == 0) return OC_OK;
+  OC_REQUIRE(table && tiles, OC_EINVAL, "oc_tile_table_build: null pointer");
+  OC_REQUIRE(((uintptr_t)tiles % 16) == 0, OC_EINVAL, "oc_tile_table_build: tiles must be 16-byte aligned");
+  OC_REQUIRE(tiles_bytes >= tile_table_bytes(n_out, K), OC_ENOMEM, "oc_tile_table_build: tiles %zu < %zu bytes",
+             tiles_bytes, tile_table_bytes(n_out, K));
+  return launch_tile_table(table, idx_bytes, table_cols, taps, K, n_out, tiles, (cudaStream_t)stream);
+}
+
+extern "C" int oc_conv_fwd_tiled(const void* data, int64_t n_in, const void* weights, int w_dtype,
+                                 int w_transposed, const void* bias, const void* tiles, int K,
+                                 int64_t n_out, int Cin, int Cout, int dtype, void* out, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+  OC_REQUIRE(tiles, OC_EINVAL, "oc_conv_fwd_tiled: null tile table");
+  // no plain table: its width only has to pass the range check, the taps are 0 .. K-1
+  return conv_fwd_impl("oc_conv_fwd_tiled", data, n_in, weights, w_dtype, w_transposed, bias, nullptr, 4,
+                       K >= 1 && K <= OC_MAX_TAPS ? K : 1, nullptr, tiles, K, n_out, Cin, Cout, dtype, out,
+                       workspace, workspace_bytes, stream);
 }
 
 extern "C" size_t oc_conv_wgrad_workspace_bytes(int K, int Cin, int Cout, int64_t n_out, int dtype) {

@@ -9,6 +9,7 @@ struct ConvArgs {
   int64_t n_in;
   const void* bias;    // (Cout) or null, same dtype as data
   const void* table;   // (n_out, table_cols) indices into data rows, < 0 = none
+  const void* tiled = nullptr;   // the same table as a tile table (tensor-core kernels only); then `table` may be null
   int idx_bytes;       // 8 or 4
   int table_cols;
   TapList taps;
@@ -43,6 +44,10 @@ int reduce_partials(const float* partial, int splits, int64_t n, float* out, cud
 
 // conv_tc.cu (tcgen05 / TMEM path, fp16 and bf16)
 bool conv_tc_supported(int K, int Cin, int Cout, int dtype);
+size_t tile_table_block_bytes(int K);
+size_t tile_table_bytes(int64_t n_out, int K);
+int launch_tile_table(const void* table, int idx_bytes, int table_cols, const TapList& taps, int K,
+                      int64_t n_out, void* out, cudaStream_t s);
 size_t conv_tc_weight_bytes(int K, int Cin, int Cout);
 int prep_weights_tc(const void* w, int w_dtype, int K, int Cin, int Cout, int transposed, int dtype,
                     void* out, cudaStream_t s);

@@ -40,7 +40,7 @@ __device__ int g_tc_status = 0;  // sticky: non-zero after any abandoned wait
 __device__ unsigned long long g_prof[64];
 #define PROF_T(v) const long long v = clock64()
 #define PROF_ADD(i, d) pr[i] += (d)
-#define PROF_DECL long long pr[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define PROF_DECL long long pr[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
 #define PROF_FLUSH(base, n) if (lane == 0) { for (int _i = 0; _i < (n); ++_i) atomicAdd(&g_prof[(base) + _i], (unsigned long long)pr[_i]); }
 #else
 #define PROF_T(v)
@@ -66,12 +66,21 @@ constexpr int N_WARPS = 5 + PROD_WARPS + (PROD_WARPS + 2) / 3;   // producers pl
 constexpr int THREADS = N_WARPS * 32;
 constexpr int MAX_STAGES = 8;
 constexpr int MAX_NT = 256;
+// Index buffer of one tile in shared memory: a 16-byte header (word 0 = mask of the taps that
+// have a valid row in this tile) followed by one 512-byte row of 128 int32 indices per tap.
+// A tile table (oc_tile_table_build) stores the tiles of a neighbour table in exactly this form,
+// so that one bulk copy per tile fetches them.
+constexpr int IDX_HDR_BYTES = 16;
+constexpr int IDX_BUF_BYTES = IDX_HDR_BYTES + OC_MAX_TAPS * TILE_M * 4;
+constexpr int LOADER_WARP = 8;            // fetches tile-table blocks (idle when a plain table is given)
 
 struct Params {
   const void* data;
   const void* wimg;    // [n_tiles_n][K][KB][NT x 128 B] swizzled weight image
   const void* bias;
   const void* table;
+  const void* tiled;   // tile table (then `table` is unused) or null
+  uint32_t tiled_block_bytes;
   void* out;
   int64_t n_out;
   int table_cols;
@@ -92,9 +101,9 @@ __host__ __device__ inline SmemLayout smem_layout(int NT, int stages) {
   L.stage_bytes = A_BYTES + NT * 128;
   L.ring = 0;
   L.sidx = L.ring + stages * L.stage_bytes;
-  L.bias = L.sidx + 2 * OC_MAX_TAPS * TILE_M * 4;
+  L.bias = L.sidx + 2 * IDX_BUF_BYTES;
   L.bars = L.bias + MAX_NT * 4;
-  L.hdr = L.bars + (2 * MAX_STAGES + 5) * 8;
+  L.hdr = L.bars + (2 * MAX_STAGES + 9) * 8;
   L.misc = L.hdr + MAX_STAGES * 4;
   L.total = L.misc + 256;
   return L;
@@ -127,9 +136,8 @@ conv_tc_kernel(const Params p) {
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const SmemLayout L = smem_layout(p.NT, p.stages);
   const uint32_t s_base = smem_u32(smem);
-  int* sidx = (int*)(smem + L.sidx);
   float* sbias = (float*)(smem + L.bias);
-  const uint32_t bars = s_base + L.bars;
+  const uint32_t bars = pin_reg(s_base + L.bars);
   volatile uint32_t* hdr = (volatile uint32_t*)(smem + L.hdr);
   uint32_t* misc = (uint32_t*)(smem + L.misc);   // [0] tmem base, [1] abort flag, [2..] warp masks (2 buffers x PROD_WARPS)
   volatile int* abort_flag = (volatile int*)(misc + 1);
@@ -140,6 +148,10 @@ conv_tc_kernel(const Params p) {
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * MAX_STAGES + a); };
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * MAX_STAGES + 2 + a); };
   const uint32_t psync_bar = bars + 8u * (2 * MAX_STAGES + 4);   // producers-only rendezvous
+  auto ifull_bar = [&](int b) { return bars + 8u * (2 * MAX_STAGES + 5 + b); };    // tile-table block b has landed
+  auto iempty_bar = [&](int b) { return bars + 8u * (2 * MAX_STAGES + 7 + b); };   // every producer warp is done with it
+  auto idx_rows = [&](int b) { return (int*)(smem + L.sidx + b * IDX_BUF_BYTES + IDX_HDR_BYTES); };
+  const bool tiled = p.tiled != nullptr;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.y * p.NT;                       // first output channel of this CTA
@@ -155,6 +167,10 @@ conv_tc_kernel(const Params p) {
       mbar_init(tempty_bar(a), 128);
     }
     mbar_init(psync_bar, PROD_THREADS);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(ifull_bar(b), 1);             // one arrive.expect_tx of the loader
+      mbar_init(iempty_bar(b), PROD_WARPS);   // lane 0 of every producer warp
+    }
     misc[1] = 0;
     fence_mbar_init();
   }
@@ -181,10 +197,13 @@ conv_tc_kernel(const Params p) {
     const int frow = pt & (TILE_M - 1);        // index prefetch: row `frow`, taps k = fpart (mod FSPLIT)
     const int fpart = pt >> 7;
     const I* table = (const I*)p.table;
-    const uint8_t* data = (const uint8_t*)p.data;
-    const uint32_t row_bytes = (uint32_t)p.Cin * 2;
-    const uint8_t* wimg = (const uint8_t*)p.wimg + (size_t)blockIdx.y * p.K * p.KB * (size_t)(p.NT * 128);
-    const uint32_t b_bytes = (uint32_t)p.NT * 128;
+    const uint8_t* data = pin_reg((const uint8_t*)p.data);
+    const uint32_t row_bytes = pin_reg((uint32_t)p.Cin * 2);
+    const uint8_t* wimg = pin_reg((const uint8_t*)p.wimg + (size_t)blockIdx.y * p.K * p.KB * (size_t)(p.NT * 128));
+    const uint32_t b_bytes = pin_reg((uint32_t)p.NT * 128);
+    // loop bounds and strides of the stage loop, pinned in registers
+    const int KB = pin_reg(p.KB), Cin = pin_reg(p.Cin), NS = pin_reg(S);
+    const uint32_t ring0 = pin_reg(s_base + L.ring), stage_bytes = pin_reg(L.stage_bytes);
     // Stages are dealt to the producer warps round-robin: a whole stage (128 rows x 8
     // chunks of 16 B) is copied by one warp, so the per-stage bookkeeping (slot wait,
     // header, weight copy, barrier arrival) is paid by one warp while the others work on
@@ -192,7 +211,7 @@ conv_tc_kernel(const Params p) {
     // rows 32 g .. 32 g + 31 of the tile, fetched 4 indices at a time.
     const int chunk = lane & 7;
     const int grp = lane >> 3;
-    const int n_own = S < PROD_WARPS ? S : PROD_WARPS;   // warps that own stages (a warp needs a slot of its own)
+    const int n_own = pin_reg(S < PROD_WARPS ? S : PROD_WARPS);   // warps that own stages (a warp needs a slot of its own)
     int owner = 0;                             // producer warp that owns the next stage
     int s = 0;                                 // ring slot of the next stage
     uint32_t ring_phase = 0;                   // flips each time the ring wraps
@@ -202,6 +221,9 @@ conv_tc_kernel(const Params p) {
     uint32_t psync_phase = 0;
     PROF_DECL;
     PROF_T(p_start);
+#ifdef OC_PROF
+    long long last_x1 = 0;
+#endif
 
     auto fetch_indices = [&](int64_t tile) {
       const int64_t r = tile * TILE_M + frow;
@@ -213,7 +235,7 @@ conv_tc_kernel(const Params p) {
     };
     auto publish_indices = [&](int buf) -> uint32_t {
       uint32_t m = 0;
-      int* dst = sidx + buf * (OC_MAX_TAPS * TILE_M);
+      int* dst = idx_rows(buf);
 #pragma unroll
       for (int i = 0; i < NF; ++i) {
         const int k = FSPLIT * i + fpart;
@@ -237,38 +259,46 @@ conv_tc_kernel(const Params p) {
     int64_t tile = blockIdx.x;
     int buf = 0;
     uint32_t mask = 0;
-    if (tile < n_tiles) {
+    uint32_t it = 0;                           // tiles done by this CTA
+    if (!tiled && tile < n_tiles) {
       fetch_indices(tile);
       mask = publish_indices(buf);
     }
-    for (; tile < n_tiles && ok; tile += gridDim.x) {
+    for (; tile < n_tiles && ok; tile += gridDim.x, ++it) {
       const int64_t next = tile + gridDim.x;
       PROF_T(pf0);
-      if (next < n_tiles) fetch_indices(next);   // loads stay in flight during this tile
+      if (tiled) {
+        buf = (int)(it & 1u);
+        if (!mbar_wait(ifull_bar(buf), (it >> 1) & 1u, abort_flag, &g_tc_status, 6)) { ok = false; break; }
+        mask = *(volatile uint32_t*)(smem + L.sidx + buf * IDX_BUF_BYTES);
+      } else if (next < n_tiles) {
+        fetch_indices(next);   // loads stay in flight during this tile
+      }
       PROF_T(pf1); PROF_ADD(3, pf1 - pf0);
       if (mask == 0) mask = 1;                   // nothing valid: one all-zero stage keeps the flow uniform
-      const int* cur = sidx + buf * (OC_MAX_TAPS * TILE_M);
+      const int* cur = idx_rows(buf);
       PROF_T(pl0);
       const uint32_t last_k = 31 - __clz(mask);
       const uint32_t first_k = __ffs(mask) - 1;
       for (uint32_t k = first_k; k <= last_k && ok; ++k) {
         if (!((mask >> k) & 1u)) continue;
-        for (int kb = 0; kb < p.KB; ++kb) {
+        for (int kb = 0; kb < KB; ++kb) {
+          PROF_T(x0);
           const bool mine = owner == pw;            // stages are dealt round-robin
           if (++owner == n_own) owner = 0;
           if (mine) {
-            PROF_T(pw0);
+            PROF_T(pw0); PROF_ADD(8, pw0 - x0);
             if (!mbar_wait(empty_bar(s), ring_phase ^ 1u, abort_flag, &g_tc_status, 1)) { ok = false; break; }
             PROF_T(pw1); PROF_ADD(0, pw1 - pw0);
-            const uint32_t a_dst = s_base + L.ring + s * L.stage_bytes;
-            const int kc = min(KBLK, p.Cin - kb * KBLK);          // channels in this block
+            const uint32_t a_dst = ring0 + s * stage_bytes;
+            const int kc = min(KBLK, Cin - kb * KBLK);          // channels in this block
             if (lane == 0) {
-              if (k == first_k && kb == 0) hdr[s] = (uint32_t)__popc(mask) * (uint32_t)p.KB;   // stages of this tile
+              if (k == first_k && kb == 0) hdr[s] = (uint32_t)__popc(mask) * (uint32_t)KB;   // stages of this tile
 #ifdef OC_NOCOPY
               mbar_arrive(full_bar(s));
 #else
               mbar_arrive_expect_tx(full_bar(s), b_bytes);
-              bulk_g2s(a_dst + A_BYTES, wimg + ((size_t)k * p.KB + kb) * b_bytes, b_bytes, full_bar(s));
+              bulk_g2s(a_dst + A_BYTES, wimg + ((size_t)k * KB + kb) * b_bytes, b_bytes, full_bar(s));
 #endif
             }
 #ifndef OC_NOCOPY
@@ -294,11 +324,17 @@ conv_tc_kernel(const Params p) {
             cp_async_arrive_noinc(full_bar(s));
             PROF_T(pw2); PROF_ADD(1, pw2 - pw1); PROF_ADD(2, 1);
           }
-          if (++s == S) { s = 0; ring_phase ^= 1u; }
+          if (++s == NS) { s = 0; ring_phase ^= 1u; }
+#ifdef OC_PROF
+          { PROF_T(x1); if (!mine) PROF_ADD(7, x1 - x0); else PROF_ADD(9, x1 - x0); if (last_x1) PROF_ADD(10, x0 - last_x1); last_x1 = x1; }
+#endif
         }
       }
       PROF_T(pl1); PROF_ADD(6, pl1 - pl0);
-      if (next < n_tiles) {
+      if (tiled) {
+        __syncwarp();                                   // every lane has read its indices of this tile
+        if (lane == 0) mbar_arrive(iempty_bar(buf));
+      } else if (next < n_tiles) {
         PROF_T(pp0);
         buf ^= 1;
         mask = publish_indices(buf);
@@ -306,8 +342,22 @@ conv_tc_kernel(const Params p) {
       }
     }
     PROF_T(p_end); PROF_ADD(5, p_end - p_start);
-    PROF_FLUSH(0, 7);
+    PROF_FLUSH(0, 12);
     cp_async_wait_all();   // nothing of this thread may still be writing shared memory at exit
+  } else if (warp == LOADER_WARP) {
+    // ===================================================================== tile-table loader
+    // One bulk copy per tile brings header + indices of the tile into one of two buffers.
+    if (tiled && lane == 0) {
+      const uint8_t* src = (const uint8_t*)p.tiled;
+      uint32_t it = 0;
+      for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+        const int b = (int)(it & 1u);
+        if (it >= 2 && !mbar_wait(iempty_bar(b), ((it >> 1) - 1u) & 1u, abort_flag, &g_tc_status, 7)) break;
+        mbar_arrive_expect_tx(ifull_bar(b), p.tiled_block_bytes);
+        bulk_g2s(s_base + L.sidx + b * IDX_BUF_BYTES, src + (size_t)tile * p.tiled_block_bytes, p.tiled_block_bytes, ifull_bar(b));
+      }
+    }
+    __syncwarp();
   } else if (warp == MMA_WARP) {
     // ===================================================================== MMA issuer
     // All 32 lanes run the loop (waits, header reads, address arithmetic) so that it is
@@ -371,7 +421,7 @@ conv_tc_kernel(const Params p) {
         acc ^= 1u;
       }
       PROF_T(m_end); PROF_ADD(4, m_end - m_start);
-      PROF_FLUSH(8, 5);
+      PROF_FLUSH(16, 5);
     }
     __syncwarp();
   } else if (warp < 4) {
@@ -408,7 +458,7 @@ conv_tc_kernel(const Params p) {
       acc_phase ^= 1u << acc;
       acc ^= 1u;
     }
-    if (warp == 0) { PROF_FLUSH(16, 3); }
+    if (warp == 0) { PROF_FLUSH(24, 3); }
   }
 
   // ------------------------------------------------------------------------ teardown
@@ -487,6 +537,52 @@ static Plan make_plan(int K, int Cin, int Cout, int dtype) {
 
 bool conv_tc_supported(int K, int Cin, int Cout, int dtype) { return tc::make_plan(K, Cin, Cout, dtype).ok; }
 
+// ---------------------------------------------------------------------------
+// tile table: the neighbour table regrouped for the tensor-core kernels.  Block t (one
+// per 128 output rows) = 16-byte header (word 0: mask of the taps with a valid entry in
+// this tile) + K rows of 128 int32 indices, row k = column taps[k] of table rows
+// 128 t .. 128 t + 127 (-1 past the end).  The kernels fetch a block with one bulk copy.
+// ---------------------------------------------------------------------------
+size_t tile_table_block_bytes(int K) { return (size_t)tc::IDX_HDR_BYTES + (size_t)K * tc::TILE_M * 4; }
+
+size_t tile_table_bytes(int64_t n_out, int K) { return (size_t)cdiv(n_out, tc::TILE_M) * tile_table_block_bytes(K); }
+
+template <typename I>
+__global__ void __launch_bounds__(tc::TILE_M)
+tile_table_kernel(const I* __restrict__ table, int table_cols, TapList taps, int K, int64_t n_out,
+                  uint8_t* __restrict__ out, uint32_t block_bytes) {
+  __shared__ uint32_t smask;
+  if (threadIdx.x == 0) smask = 0;
+  __syncthreads();
+  const int64_t tile = blockIdx.x;
+  const int64_t r = tile * tc::TILE_M + threadIdx.x;
+  uint8_t* blk = out + (size_t)tile * block_bytes;
+  int* rows = (int*)(blk + tc::IDX_HDR_BYTES);
+  uint32_t m = 0;
+  for (int k = 0; k < K; ++k) {
+    const int v = r < n_out ? (int)table[r * table_cols + taps.t[k]] : -1;
+    rows[k * tc::TILE_M + threadIdx.x] = v < 0 ? -1 : v;
+    m |= (v >= 0 ? 1u : 0u) << k;
+  }
+  m = __reduce_or_sync(0xffffffffu, m);
+  if ((threadIdx.x & 31) == 0 && m) atomicOr(&smask, m);
+  __syncthreads();
+  if (threadIdx.x < 4) ((uint32_t*)blk)[threadIdx.x] = threadIdx.x == 0 ? smask : 0u;
+}
+
+int launch_tile_table(const void* table, int idx_bytes, int table_cols, const TapList& taps, int K,
+                      int64_t n_out, void* out, cudaStream_t s) {
+  if (n_out == 0) return OC_OK;
+  const unsigned grid = (unsigned)cdiv(n_out, tc::TILE_M);
+  const uint32_t bb = (uint32_t)tile_table_block_bytes(K);
+  if (idx_bytes == 8)
+    tile_table_kernel<int64_t><<<grid, tc::TILE_M, 0, s>>>((const int64_t*)table, table_cols, taps, K, n_out, (uint8_t*)out, bb);
+  else
+    tile_table_kernel<int32_t><<<grid, tc::TILE_M, 0, s>>>((const int32_t*)table, table_cols, taps, K, n_out, (uint8_t*)out, bb);
+  OC_LAUNCH_OK("tile_table_kernel");
+  return OC_OK;
+}
+
 size_t conv_tc_weight_bytes(int K, int Cin, int Cout) {
   const tc::Plan P = tc::make_plan(K, Cin, Cout, OC_F16);
   return (size_t)P.n_tiles_n * K * P.KB * P.NT * 128;
@@ -539,6 +635,8 @@ int launch_conv_tc(const ConvArgs& a, const void* Wimg, int* status_dev, cudaStr
   if (a.n_out == 0) return OC_OK;
   tc::Params prm;
   prm.data = a.data; prm.wimg = Wimg; prm.bias = a.bias; prm.table = a.table; prm.out = a.out;
+  prm.tiled = a.tiled; prm.tiled_block_bytes = (uint32_t)tile_table_block_bytes(a.K);
+  OC_REQUIRE(((uintptr_t)a.tiled % 16) == 0, OC_EINVAL, "conv_tc: the tile table must be 16-byte aligned");
   prm.n_out = a.n_out; prm.table_cols = a.table_cols; prm.K = a.K; prm.Cin = a.Cin; prm.Cout = a.Cout;
   prm.KB = P.KB; prm.NT = P.NT; prm.stages = P.stages; prm.tmem_cols = P.tmem_cols; prm.taps = a.taps;
   const bool bf = a.dtype == OC_BF16;

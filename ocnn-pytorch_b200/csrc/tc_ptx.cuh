@@ -196,6 +196,14 @@ __host__ __device__ __forceinline__ uint32_t make_idesc(int bf16, int a_mn_major
          ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
+// Pins a value in a register.  Kernel parameters and values derived from them are otherwise
+// re-read from the constant bank wherever they are used; in a warp that has just queued
+// dozens of cp.async instructions such a load waits behind them (~300 cycles measured on the
+// back edge of the producer loop).
+__device__ __forceinline__ uint32_t pin_reg(uint32_t v) { asm volatile("" : "+r"(v)); return v; }
+__device__ __forceinline__ int pin_reg(int v) { asm volatile("" : "+r"(v)); return v; }
+__device__ __forceinline__ const uint8_t* pin_reg(const uint8_t* v) { asm volatile("" : "+l"(v)); return v; }
+
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

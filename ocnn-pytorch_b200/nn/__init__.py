@@ -1,6 +1,7 @@
 from .octree_pad import octree_pad, octree_depad
 from .octree_conv import (OctreeConv, OctreeDeconv, octree_conv, octree_deconv,
-                          OctreeConvFunction, OctreeDeconvFunction, conv_gather, conv_wgrad)
+                          OctreeConvFunction, OctreeDeconvFunction, conv_gather, conv_wgrad,
+                          tile_table, tiled_supported)
 from .octree_dwconv import OctreeDWConv, octree_dwconv
 from .octree_pool import (octree_max_pool, octree_max_unpool, OctreeMaxPool, OctreeMaxUnpool)
 from .octree_interp import octree_nearest_upsample, OctreeUpsample
@@ -9,7 +10,7 @@ from .octree_norm import (OctreeBatchNorm, OctreeGroupNorm, OctreeInstanceNorm, 
 
 __all__ = [
     'octree_pad', 'octree_depad', 'OctreeConv', 'OctreeDeconv', 'octree_conv', 'octree_deconv',
-    'OctreeConvFunction', 'OctreeDeconvFunction', 'conv_gather', 'conv_wgrad', 'OctreeDWConv',
+    'OctreeConvFunction', 'OctreeDeconvFunction', 'conv_gather', 'conv_wgrad', 'tile_table', 'tiled_supported', 'OctreeDWConv',
     'octree_dwconv', 'octree_max_pool', 'octree_max_unpool', 'OctreeMaxPool', 'OctreeMaxUnpool',
     'octree_nearest_upsample', 'OctreeUpsample', 'OctreeBatchNorm', 'OctreeGroupNorm',
     'OctreeInstanceNorm', 'OctreeNorm', 'convert_sync_batchnorm', 'col_stats',

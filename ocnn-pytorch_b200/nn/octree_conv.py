@@ -20,10 +20,31 @@ def _idx_bytes(table):
   return 8 if table.dtype == torch.int64 else 4
 
 
-def conv_gather(data, weights, w_transposed, bias, table, taps, c_in, c_out):
+def tiled_supported(K, c_in, c_out, dtype):
+  r''' True where the convolution runs on the tensor-core kernel, which can take the
+  table as a tile table (:func:`tile_table`). '''
+  return dtype in (torch.float16, torch.bfloat16) and \
+      bool(_lib.lib().oc_conv_tiled_supported(K, c_in, c_out, _lib.dtype_code(dtype)))
+
+
+def tile_table(table, taps):
+  r''' Regroups columns `taps` of a neighbour table into blocks of 128 rows (16-byte
+  header with the mask of non-empty taps, then one row of 128 int32 per tap): the form
+  the tensor-core kernel fetches with one bulk copy per tile.  Returns a uint8 tensor. '''
+  _lib.require_cuda(table)
+  K, n_out = len(taps), table.shape[0]
+  tiles = torch.empty(_lib.lib().oc_tile_table_bytes(n_out, K), dtype=torch.uint8, device=table.device)
+  _lib.call('oc_tile_table_build', _lib.ptr(table), _idx_bytes(table), table.shape[1],
+            _lib.int_array(taps), K, n_out, _lib.ptr(tiles), tiles.numel(), _lib.stream(table.device))
+  return tiles
+
+
+def conv_gather(data, weights, w_transposed, bias, table, taps, c_in, c_out, tiles=None):
   r''' ``out[r] = sum_k data[table[r, taps[k]]] @ Wk (+ bias)`` with
   ``Wk = weights[k]`` (``w_transposed=False``, weights ``(K, c_in, c_out)``) or
-  ``weights[k].T`` (``w_transposed=True``, weights ``(K, c_out, c_in)``). '''
+  ``weights[k].T`` (``w_transposed=True``, weights ``(K, c_out, c_in)``).
+  `tiles`: ``tile_table(table, taps)``, used instead of `table` where
+  :func:`tiled_supported` holds. '''
   _lib.require_cuda(data, weights, table)
   data = data.contiguous()
   weights = weights.contiguous()
@@ -37,6 +58,12 @@ def conv_gather(data, weights, w_transposed, bias, table, taps, c_in, c_out):
   dt = _lib.dtype_code(data.dtype)
   out = torch.empty(n_out, c_out, dtype=data.dtype, device=data.device)
   ws = _lib.workspace(_lib.lib().oc_conv_workspace_bytes(K, c_in, c_out, dt), data.device)
+  if tiles is not None and n_out > 0 and tiled_supported(K, c_in, c_out, data.dtype):
+    _lib.call('oc_conv_fwd_tiled', _lib.ptr(data), data.shape[0], _lib.ptr(weights),
+              _lib.dtype_code(weights.dtype), int(w_transposed), _lib.ptr(bias), _lib.ptr(tiles), K,
+              n_out, c_in, c_out, dt, _lib.ptr(out), _lib.ptr(ws), ws.numel(),
+              _lib.stream(data.device))
+    return out
   _lib.call('oc_conv_fwd', _lib.ptr(data), data.shape[0], _lib.ptr(weights),
             _lib.dtype_code(weights.dtype), int(w_transposed), _lib.ptr(bias), _lib.ptr(table),
             _idx_bytes(table), table.shape[1], _lib.int_array(taps), K, n_out, c_in, c_out, dt,
@@ -125,6 +152,14 @@ class _OctreeDeconv(OctreeConvBase):
   def is_conv_layer(self): return False
 
 
+def _tiles(octree, depth, kernel, stride, nempty, transposed, K, c_in, c_out, data):
+  r''' The octree's cached tile table of this convolution, or None where the
+  tensor-core kernel does not apply (then the plain table is used). '''
+  if not tiled_supported(K, c_in, c_out, data.dtype):
+    return None
+  return octree.conv_tiles(depth, kernel, stride, nempty, transposed)
+
+
 class OctreeConvFunction(Function):
   r''' Octree convolution with autograd (octree_conv.py:219-254). '''
 
@@ -136,7 +171,8 @@ class OctreeConvFunction(Function):
     conv.check(data)
     table, taps = octree.conv_table(depth, conv.kernel, stride, nempty)
     assert table.shape[0] == conv.out_h
-    out = conv_gather(data, weights, False, bias, table, taps, in_channels, out_channels)
+    tiles = _tiles(octree, depth, conv.kernel, stride, nempty, False, len(taps), in_channels, out_channels, data)
+    out = conv_gather(data, weights, False, bias, table, taps, in_channels, out_channels, tiles)
     ctx.save_for_backward(data, weights)
     ctx.conf = (octree, depth, conv.kernel, stride, nempty, in_channels, out_channels,
                 bias is not None)
@@ -150,7 +186,8 @@ class OctreeConvFunction(Function):
     grad_in = grad_w = grad_b = None
     if ctx.needs_input_grad[0]:
       table_t, taps_t = octree.conv_table_transposed(depth, kernel, stride, nempty)
-      grad_in = conv_gather(grad, weights, True, None, table_t, taps_t, cout, cin)
+      tiles = _tiles(octree, depth, kernel, stride, nempty, True, len(taps_t), cout, cin, grad)
+      grad_in = conv_gather(grad, weights, True, None, table_t, taps_t, cout, cin, tiles)
     if ctx.needs_input_grad[1] or (has_bias and ctx.needs_input_grad[2]):
       table, taps = octree.conv_table(depth, kernel, stride, nempty)
       gw, gb = conv_wgrad(data, grad, table, taps, cin, cout, has_bias and ctx.needs_input_grad[2])
@@ -171,7 +208,8 @@ class OctreeDeconvFunction(Function):
     nd = deconv.neigh_depth
     table_t, taps_t = octree.conv_table_transposed(nd, deconv.kernel, stride, nempty)
     assert table_t.shape[0] == deconv.out_h
-    out = conv_gather(data, weights, True, bias, table_t, taps_t, in_channels, out_channels)
+    tiles = _tiles(octree, nd, deconv.kernel, stride, nempty, True, len(taps_t), in_channels, out_channels, data)
+    out = conv_gather(data, weights, True, bias, table_t, taps_t, in_channels, out_channels, tiles)
     ctx.save_for_backward(data, weights)
     ctx.conf = (octree, nd, deconv.kernel, stride, nempty, in_channels, out_channels,
                 bias is not None)
@@ -185,7 +223,8 @@ class OctreeDeconvFunction(Function):
     grad_in = grad_w = grad_b = None
     table, taps = octree.conv_table(nd, kernel, stride, nempty)
     if ctx.needs_input_grad[0]:
-      grad_in = conv_gather(grad, weights, False, None, table, taps, cout, cin)
+      tiles = _tiles(octree, nd, kernel, stride, nempty, False, len(taps), cout, cin, grad)
+      grad_in = conv_gather(grad, weights, False, None, table, taps, cout, cin, tiles)
     if ctx.needs_input_grad[1]:
       # weights are (K, out_channels, in_channels): gathered operand = grad
       gw, _ = conv_wgrad(grad, data, table, taps, cout, cin, False)

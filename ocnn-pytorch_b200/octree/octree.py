@@ -380,6 +380,17 @@ class Octree:
       self._table_cache[key] = inv
     return self._table_cache[key], list(range(len(taps)))
 
+  def conv_tiles(self, depth: int, kernel: str, stride: int, nempty: bool, transposed: bool = False):
+    r''' The table of :meth:`conv_table` (or :meth:`conv_table_transposed`) as a tile
+    table for the tensor-core convolution kernel, built once and cached like the
+    neighbour tables themselves. '''
+    key = ('tiles', depth, kernel, stride, nempty, transposed)
+    if key not in self._table_cache:
+      from ..nn.octree_conv import tile_table
+      table, taps = (self.conv_table_transposed if transposed else self.conv_table)(depth, kernel, stride, nempty)
+      self._table_cache[key] = tile_table(table, taps)
+    return self._table_cache[key]
+
   def batch_offsets(self, depth: int, nempty: bool = False):
     r''' Host list of batch_size+1 row offsets of each octree at :attr:`depth`
     (rows of one octree are contiguous because keys sort batch-major). '''

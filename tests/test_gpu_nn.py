@@ -149,6 +149,45 @@ def test_conv333_vs_oracle_half(mid_octree, cin, cout, nempty, dtype):
   assert_close(to_np(m.weights.grad), egw, TOL16, 'gw')
 
 
+def test_tile_table_layout_and_equivalence(mid_octree):
+  # The tile table is the neighbour table regrouped in blocks of 128 rows; a convolution
+  # given the tile table returns bit-for-bit what it returns given the plain table.
+  octree, o = mid_octree
+  for d, kernel, stride, nempty, transposed in [(6, '333', 1, False, False), (6, '333', 1, True, True),
+                                                (5, '313', 1, False, False), (6, '222', 2, False, False),
+                                                (6, '333', 2, True, True), (3, '333', 1, False, False)]:
+    table, taps = (octree.conv_table_transposed if transposed else octree.conv_table)(d, kernel, stride, nempty)
+    tiles = octree.conv_tiles(d, kernel, stride, nempty, transposed)
+    assert octree.conv_tiles(d, kernel, stride, nempty, transposed) is tiles      # cached
+    K, n_out = len(taps), table.shape[0]
+    nt = (n_out + 127) // 128
+    blk = 16 + K * 512
+    assert tiles.dtype == torch.uint8 and tiles.numel() == nt * blk
+    raw = to_np(tiles).reshape(nt, blk)
+    hdr = raw[:, :16].copy().view(np.uint32)
+    rows = raw[:, 16:].copy().view(np.int32).reshape(nt, K, 128)
+    want = np.full((nt * 128, K), -1, np.int64)
+    want[:n_out] = to_np(table)[:, taps]
+    want = np.where(want < 0, -1, want).reshape(nt, 128, K).transpose(0, 2, 1)
+    assert np.array_equal(rows, want)
+    mask = ((want >= 0).any(axis=2) * (1 << np.arange(K))[None, :]).sum(axis=1)
+    assert np.array_equal(hdr[:, 0], mask.astype(np.uint32)) and not hdr[:, 1:].any()
+    n_in = int(to_np(table).max()) + 1
+    for dtype, cin, cout in [(torch.float16, 64, 64), (torch.bfloat16, 32, 80), (torch.float16, 144, 16)]:
+      assert b200.nn.tiled_supported(K, cin, cout, dtype)
+      g = torch.Generator(device=dev()).manual_seed(d * 100 + cin)
+      x = torch.randn(n_in, cin, device=dev(), generator=g).to(dtype)
+      w = (torch.randn(K, cin, cout, device=dev(), generator=g) / (K * cin) ** 0.5).to(dtype)
+      bias = torch.randn(cout, device=dev(), generator=g).to(dtype)
+      y_plain = b200.nn.conv_gather(x, w, False, bias, table, taps, cin, cout)
+      y_tiled = b200.nn.conv_gather(x, w, False, bias, table, taps, cin, cout, tiles=tiles)
+      assert torch.equal(y_plain, y_tiled)
+  b200._lib.status_check(dev())
+  # shapes off the tensor-core path have no tiled form: the plain table is used
+  assert not b200.nn.tiled_supported(27, 30, 64, torch.float16)
+  assert not b200.nn.tiled_supported(27, 64, 64, torch.float32)
+
+
 def test_conv_is_deterministic_and_linear(mid_octree):
   octree, o = mid_octree
   d, C = 6, 64
