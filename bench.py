@@ -361,7 +361,7 @@ def run_conv_only(args, b200, octree, dev):
   parts = {}
   for name, fn in (('fwd', lambda: b200.nn.conv_gather(xd, conv.weights, False, None, table, taps, CH, CH, tiles)),
                    ('dgrad', lambda: b200.nn.conv_gather(gy, conv.weights, True, None, table_t, taps_t, CH, CH, tiles_t)),
-                   ('wgrad', lambda: b200.nn.conv_wgrad(xd, gy, table, taps, CH, CH))):
+                   ('wgrad', lambda: b200.nn.conv_wgrad(xd, gy, table, taps, CH, CH, False, tiles))):
     fn()
     torch.cuda.synchronize()
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -426,7 +426,7 @@ def run_suite(args, b200, octree, dev):
         tl, tl_t = octree.conv_tiles(D, '333', 1, nempty), octree.conv_tiles(D, '333', 1, nempty, True)
         emit('conv333_fwd', _time(lambda: b200.nn.conv_gather(x, w, False, None, table, taps, C, C, tl)), flops=fl, **tag)
         emit('conv333_dgrad', _time(lambda: b200.nn.conv_gather(gy, w, True, None, table_t, taps_t, C, C, tl_t)), flops=fl, **tag)
-        emit('conv333_wgrad', _time(lambda: b200.nn.conv_wgrad(x, gy, table, taps, C, C)), flops=fl, **tag)
+        emit('conv333_wgrad', _time(lambda: b200.nn.conv_wgrad(x, gy, table, taps, C, C, False, tl)), flops=fl, **tag)
         del x, gy
   # strided / transposed path (bf16), depth-wise conv, pooling, upsampling, normalisation
   n8, n7 = int(octree.nnum[D]), int(octree.nnum[D - 1])

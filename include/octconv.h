@@ -191,6 +191,12 @@ int oc_conv_wgrad(const void* data, int64_t n_in, const void* grad_out, int64_t 
                   const void* table, int idx_bytes, int table_cols, const int* h_taps, int K,
                   int Cin, int Cout, int dtype, float* grad_w, float* grad_bias,
                   void* workspace, size_t workspace_bytes, void* stream);
+/* oc_conv_wgrad with the table given as a tile table (see oc_tile_table_build); same
+ * workspace size.  Given a plain table, oc_conv_wgrad regroups it into the workspace on
+ * every call where the tensor-core kernel applies, so the tile table saves that pass. */
+int oc_conv_wgrad_tiled(const void* data, int64_t n_in, const void* grad_out, int64_t n_out,
+                        const void* tiles, int K, int Cin, int Cout, int dtype, float* grad_w,
+                        float* grad_bias, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Depth-wise convolution, ocnn/nn/octree_dwconv.py:30-118:
  *   out[r, c] = sum_k data[table[r, taps[k]], c] * w[k, c]     (weights fp32 (K,C))

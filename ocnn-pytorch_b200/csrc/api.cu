@@ -189,28 +189,34 @@ extern "C" size_t oc_conv_wgrad_workspace_bytes(int K, int Cin, int Cout, int64_
   return wgrad_plan(K, Cin, Cout, n_out, dtype).total;
 }
 
-extern "C" int oc_conv_wgrad(const void* data, int64_t n_in, const void* grad_out, int64_t n_out,
-                             const void* table, int idx_bytes, int table_cols, const int* h_taps,
-                             int K, int Cin, int Cout, int dtype, float* grad_w, float* grad_bias,
-                             void* workspace, size_t workspace_bytes, void* stream) {
-  int rc = check_conv_common("oc_conv_wgrad", K, Cin, Cout, dtype, idx_bytes, table_cols, n_in, n_out);
+static int conv_wgrad_impl(const char* who, const void* data, int64_t n_in, const void* grad_out, int64_t n_out,
+                           const void* table, int idx_bytes, int table_cols, const int* h_taps, const void* tiles,
+                           int K, int Cin, int Cout, int dtype, float* grad_w, float* grad_bias,
+                           void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_conv_common(who, K, Cin, Cout, dtype, idx_bytes, table_cols, n_in, n_out);
   if (rc) return rc;
   WgradArgs a;
-  rc = make_taps(h_taps, K, table_cols, &a.taps, "oc_conv_wgrad");
-  if (rc) return rc;
-  OC_REQUIRE(grad_w, OC_EINVAL, "oc_conv_wgrad: null grad_w");
+  if (tiles) {
+    for (int k = 0; k < K; ++k) a.taps.t[k] = k;
+  } else {
+    rc = make_taps(h_taps, K, table_cols, &a.taps, who);
+    if (rc) return rc;
+  }
+  OC_REQUIRE(grad_w, OC_EINVAL, "%s: null grad_w", who);
   cudaStream_t s = (cudaStream_t)stream;
   if (n_out == 0) {
     OC_CUDA_OK(cudaMemsetAsync(grad_w, 0, (size_t)K * Cin * Cout * 4, s));
     if (grad_bias) OC_CUDA_OK(cudaMemsetAsync(grad_bias, 0, (size_t)Cout * 4, s));
     return OC_OK;
   }
-  OC_REQUIRE(grad_out && table && workspace, OC_EINVAL, "oc_conv_wgrad: null pointer");
-  OC_REQUIRE(data || n_in == 0, OC_EINVAL, "oc_conv_wgrad: null data");
+  OC_REQUIRE(grad_out && (table || tiles) && workspace, OC_EINVAL, "%s: null pointer", who);
+  OC_REQUIRE(data || n_in == 0, OC_EINVAL, "%s: null data", who);
   const WgradPlan P = wgrad_plan(K, Cin, Cout, n_out, dtype);
-  OC_REQUIRE(workspace_bytes >= P.total, OC_ENOMEM, "oc_conv_wgrad: workspace %zu < %zu bytes",
-             workspace_bytes, P.total);
-  a.data = data; a.n_in = n_in; a.grad_out = grad_out; a.n_out = n_out; a.table = table;
+  OC_REQUIRE(P.tc || !tiles, OC_EINVAL,
+             "%s: a tile table needs fp16/bf16 data and channel counts that are multiples of 16 "
+             "(ask oc_conv_tiled_supported); use oc_conv_wgrad with the plain table", who);
+  OC_REQUIRE(workspace_bytes >= P.total, OC_ENOMEM, "%s: workspace %zu < %zu bytes", who, workspace_bytes, P.total);
+  a.data = data; a.n_in = n_in; a.grad_out = grad_out; a.n_out = n_out; a.table = table; a.tiled = tiles;
   a.idx_bytes = idx_bytes; a.table_cols = table_cols; a.K = K; a.Cin = Cin; a.Cout = Cout; a.dtype = dtype;
   char* ws = (char*)workspace;
   if (P.tc) {
@@ -225,4 +231,21 @@ extern "C" int oc_conv_wgrad(const void* data, int64_t n_in, const void* grad_ou
     rc = launch_colstats(grad_out, nullptr, n_out, Cout, dtype, grad_bias, nullptr, ws + P.stats_off,
                          P.stats_bytes, s);
   return rc;
+}
+
+extern "C" int oc_conv_wgrad(const void* data, int64_t n_in, const void* grad_out, int64_t n_out,
+                             const void* table, int idx_bytes, int table_cols, const int* h_taps,
+                             int K, int Cin, int Cout, int dtype, float* grad_w, float* grad_bias,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+  return conv_wgrad_impl("oc_conv_wgrad", data, n_in, grad_out, n_out, table, idx_bytes, table_cols, h_taps,
+                         nullptr, K, Cin, Cout, dtype, grad_w, grad_bias, workspace, workspace_bytes, stream);
+}
+
+extern "C" int oc_conv_wgrad_tiled(const void* data, int64_t n_in, const void* grad_out, int64_t n_out,
+                                   const void* tiles, int K, int Cin, int Cout, int dtype, float* grad_w,
+                                   float* grad_bias, void* workspace, size_t workspace_bytes, void* stream) {
+  OC_REQUIRE(tiles, OC_EINVAL, "oc_conv_wgrad_tiled: null tile table");
+  return conv_wgrad_impl("oc_conv_wgrad_tiled", data, n_in, grad_out, n_out, nullptr, 4,
+                         K >= 1 && K <= OC_MAX_TAPS ? K : 1, nullptr, tiles, K, Cin, Cout, dtype, grad_w,
+                         grad_bias, workspace, workspace_bytes, stream);
 }

@@ -26,6 +26,7 @@ struct WgradArgs {
   const void* grad_out;  // (n_out, Cout)
   int64_t n_out;
   const void* table;
+  const void* tiled = nullptr;   // the same table as a tile table (tensor-core kernel only); then `table` may be null
   int idx_bytes;
   int table_cols;
   TapList taps;

@@ -15,7 +15,12 @@
 // tiles of its slice; per tile it loads grad_out once and, for every M tile of its
 // group with at least one valid neighbour, gathers the two blocks and issues
 // 8 MMAs (K = 16 rows each) into that M tile's own TMEM accumulator, which stays
-// resident for the whole slice.  At the end every accumulator is written to a
+// resident for the whole slice.
+// Roles: a loader warp brings in, per row tile, the tile-table block (one bulk copy) and
+// the grad_out tile; eight producer warps gather, each owning whole 64-channel blocks
+// dealt round-robin (so a warp keeps a block of its own in flight while the others work
+// on theirs); one warp issues the MMAs.  The neighbour table always comes as a tile table
+// (oc_tile_table_build); the entry point builds one in the workspace when given a plain table.  At the end every accumulator is written to a
 // per-slice fp32 partial and a second kernel adds the slices in a fixed order
 // (no atomics: the result does not vary from run to run).
 // (Included at the end of conv_tc.cu: both kernels share the sticky status word,
@@ -35,6 +40,7 @@ constexpr int PROD_THREADS = PROD_WARPS * 32;
 // Warps 0-3: no main-loop role (epilogue at the end); warp 4: MMA issuer; producers: warps > 4
 // whose index is not a multiple of 4, so that the MMA warp's SM sub-partition holds no producer.
 constexpr int MMA_WARP = 4;
+constexpr int LOADER_WARP = 8;
 constexpr int N_WARPS = 5 + PROD_WARPS + (PROD_WARPS + 2) / 3;
 constexpr int THREADS = N_WARPS * 32;
 constexpr int MAX_STAGES = 6;
@@ -43,11 +49,11 @@ constexpr int MAX_MT = 16;                // M tiles (accumulators) per CTA
 struct Params {
   const void* data;
   const void* gout;
-  const void* table;
+  const void* tiled;    // tile table of the K taps
+  uint32_t tiled_block_bytes;
   float* partial;       // [row slices][K][Cin][Cout]
   int64_t n_out;
   int64_t tiles_per_slice;
-  int table_cols;
   int K, Cin, Cout;
   int KB;               // 64-channel blocks per tap
   int nblk;             // K * KB
@@ -56,7 +62,6 @@ struct Params {
   int mt_per_cta;
   int stages;
   int tmem_cols;
-  TapList taps;
 };
 
 struct SmemLayout {
@@ -68,23 +73,22 @@ __host__ __device__ inline SmemLayout smem_layout(int GB, int stages) {
   L.ring = 0;                                     // stages x 2 blocks
   L.gbuf = L.ring + stages * 2 * BLK_BYTES;       // 2 buffers x GB blocks
   L.sidx = L.gbuf + 2 * GB * BLK_BYTES;
-  L.bars = L.sidx + 2 * OC_MAX_TAPS * TILE_R * 4;
-  L.hdr = L.bars + (2 * MAX_STAGES + 6) * 8;
+  L.bars = L.sidx + 2 * IDX_BUF_BYTES;
+  L.hdr = L.bars + (2 * MAX_STAGES + 9) * 8;
   L.misc = L.hdr + MAX_STAGES * 4;
   L.total = L.misc + 128;
   return L;
 }
 
-template <bool BF16, typename I>
+template <bool BF16>
 __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const SmemLayout L = smem_layout(p.GB, p.stages);
   const uint32_t s_base = smem_u32(smem);
-  int* sidx = (int*)(smem + L.sidx);
-  const uint32_t bars = s_base + L.bars;
+  const uint32_t bars = pin_reg(s_base + L.bars);
   volatile uint32_t* hdr = (volatile uint32_t*)(smem + L.hdr);
-  uint32_t* misc = (uint32_t*)(smem + L.misc);   // [0] tmem base, [1] abort, [2..17] warp masks, [18] touched
+  uint32_t* misc = (uint32_t*)(smem + L.misc);   // [0] tmem base, [1] abort, [18] touched
   volatile int* abort_flag = (volatile int*)(misc + 1);
 
   const int S = p.stages;
@@ -92,8 +96,9 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
   auto empty_bar = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
   auto gfull_bar = [&](int g) { return bars + 8u * (2 * MAX_STAGES + g); };
   auto gempty_bar = [&](int g) { return bars + 8u * (2 * MAX_STAGES + 2 + g); };
-  const uint32_t psync_bar = bars + 8u * (2 * MAX_STAGES + 4);
-  const uint32_t done_bar = bars + 8u * (2 * MAX_STAGES + 5);
+  auto ifull_bar = [&](int b) { return bars + 8u * (2 * MAX_STAGES + 4 + b); };    // tile-table block b has landed
+  auto iempty_bar = [&](int b) { return bars + 8u * (2 * MAX_STAGES + 6 + b); };   // every producer warp is done with it
+  const uint32_t done_bar = bars + 8u * (2 * MAX_STAGES + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slice = blockIdx.x;
@@ -107,14 +112,15 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(full_bar(s), PROD_THREADS + 1);
+      mbar_init(full_bar(s), 64 + 1);   // the lanes of the two warps that own the stage's blocks + the header writer
       mbar_init(empty_bar(s), 1);
     }
     for (int g = 0; g < 2; ++g) {
-      mbar_init(gfull_bar(g), PROD_THREADS);
+      mbar_init(gfull_bar(g), 32);      // the lanes of the loader warp
       mbar_init(gempty_bar(g), 1);
+      mbar_init(ifull_bar(g), 1);
+      mbar_init(iempty_bar(g), PROD_WARPS);
     }
-    mbar_init(psync_bar, PROD_THREADS);
     mbar_init(done_bar, 1);
     misc[1] = 0;
     misc[18] = 0;
@@ -129,165 +135,140 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
   tc_fence_after();
   const uint32_t tmem_base = misc[0];
 
-  // taps that feed this CTA's M tiles
-  uint32_t group_taps = 0;
-  for (int b = 2 * m_lo; b < 2 * (m_lo + m_cnt) && b < p.nblk; ++b) group_taps |= 1u << (b / p.KB);
-
   const int pw_raw = (warp - 5) - ((warp - 5) >> 2);
   if (warp > 4 && (warp & 3) != 0 && pw_raw < PROD_WARPS) {
     // ===================================================================== producers
     const int pw = pw_raw;
-    const int pt = pw * 32 + lane;
-    const int frow = pt & (TILE_R - 1);
-    const int fhalf = pt >> 7;
-    const I* table = (const I*)p.table;
-    const uint8_t* data = (const uint8_t*)p.data;
-    const uint8_t* gout = (const uint8_t*)p.gout;
-    const uint32_t row_bytes = (uint32_t)p.Cin * 2;
-    const uint32_t grow_bytes = (uint32_t)p.Cout * 2;
+    const uint8_t* data = pin_reg((const uint8_t*)p.data);
+    const uint32_t row_bytes = pin_reg((uint32_t)p.Cin * 2);
+    const int KB = pin_reg(p.KB), Cin = pin_reg(p.Cin), NS = pin_reg(S), nblk = pin_reg(p.nblk);
+    const uint32_t ring0 = pin_reg(s_base + L.ring);
     const int chunk = lane & 7;
-    const int row0 = pw * 16 + (lane >> 3) * 4;
-    uint32_t doff[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) doff[j] = (uint32_t)((row0 + j) * 128 + ((chunk ^ ((row0 + j) & 7)) << 4));
+    const int grp = lane >> 3;
+    // taps that feed this CTA's M tiles
+    uint32_t group_taps = 0;
+    for (int b = 2 * m_lo; b < 2 * (m_lo + m_cnt) && b < nblk; ++b) group_taps |= 1u << (b / KB);
     int s = 0;
     uint32_t ring_phase = 0;
-    uint32_t gb_sel = 0, g_phase[2] = {0, 0};
-    constexpr int NF = (OC_MAX_TAPS + 1) / 2;
-    int nidx[NF];
+    int owner = 0;                 // producer warp that owns the next block
     bool ok = true;
-    uint32_t psync_phase = 0;
     uint32_t touched = 0;
 
-    auto fetch_indices = [&](int64_t tile) {
-      const int64_t r = tile * TILE_R + frow;
+    // Copies one 64-channel block (128 rows) of tap row `irow` (null: no valid row, zeros):
+    // 8 lanes copy one 128-byte row; lane group `grp` owns rows 32 grp .. 32 grp + 31.
+    auto gather_block = [&](uint32_t dst, const int* irow, int kb) {
+      const bool live = chunk * 8 < min(64, Cin - kb * 64);   // channels past Cin: zeros
+      const uint8_t* lane_src = data + (size_t)kb * 128 + chunk * 16;
 #pragma unroll
-      for (int i = 0; i < NF; ++i) {
-        const int k = 2 * i + fhalf;
-        const bool want = k < p.K && ((group_taps >> k) & 1u) && r < p.n_out;
-        nidx[i] = want ? (int)table[r * p.table_cols + p.taps.t[k < OC_MAX_TAPS ? k : 0]] : -1;
-      }
-    };
-    auto publish_indices = [&](int buf) -> uint32_t {
-      uint32_t m = 0;
-      int* dst = sidx + buf * (OC_MAX_TAPS * TILE_R);
-#pragma unroll
-      for (int i = 0; i < NF; ++i) {
-        const int k = 2 * i + fhalf;
-        if (k < OC_MAX_TAPS) {
-          dst[k * TILE_R + frow] = nidx[i];
-          m |= (nidx[i] >= 0 ? 1u : 0u) << k;
-        }
-      }
-      m = __reduce_or_sync(0xffffffffu, m);
-      if (lane == 0) misc[2 + pw + PROD_WARPS * buf] = m;
-      mbar_arrive(psync_bar);
-      if (!mbar_wait(psync_bar, psync_phase, abort_flag, &g_tc_status, 15)) ok = false;
-      psync_phase ^= 1u;
-      uint32_t all = 0;
-#pragma unroll
-      for (int w = 0; w < PROD_WARPS; ++w) all |= misc[2 + w + PROD_WARPS * buf];
-      return all;
-    };
-    // copies the 4 rows of this lane for one 64-channel block; rid < 0 -> zeros
-    auto gather_block = [&](uint32_t dst, const int (&rid)[4], int kb) {
-      const int kc = min(64, p.Cin - kb * 64);
-      if (chunk * 8 < kc) {
-        const uint8_t* lane_src = data + (size_t)kb * 128 + chunk * 16;
+      for (int q = 0; q < 8; ++q) {
+        int4 r4 = make_int4(-1, -1, -1, -1);
+        if (irow != nullptr && live) r4 = *reinterpret_cast<const int4*>(irow + grp * 32 + 4 * q);
+        const int rid[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
+          const int r = grp * 32 + 4 * q + j;
           const int idx = rid[j];
-          cp_async_16(dst + doff[j], lane_src + (size_t)(idx < 0 ? 0 : idx) * row_bytes, idx >= 0 ? 16u : 0u);
+          cp_async_16(dst + r * 128 + ((chunk ^ ((4 * q + j) & 7)) << 4),
+                      lane_src + (size_t)(idx < 0 ? 0 : idx) * row_bytes, idx >= 0 ? 16u : 0u);
         }
-      } else {
-        // channels past Cin would otherwise hold stale shared memory: they end up in
-        // accumulator rows that are never stored, but must not be NaN-producing garbage
-#pragma unroll
-        for (int j = 0; j < 4; ++j) cp_async_16(dst + doff[j], data, 0u);
       }
     };
 
-    int64_t tile = t_begin;
-    int buf = 0;
-    uint32_t mask = 0;
-    if (tile < t_end) {
-      fetch_indices(tile);
-      mask = publish_indices(buf);
-    }
-    for (; tile < t_end && ok; ++tile) {
-      const int64_t next = tile + 1;
-      if (next < t_end) fetch_indices(next);
-      const int* cur = sidx + buf * (OC_MAX_TAPS * TILE_R);
-      if (mask != 0) {
-        // ---- grad_out tile: dense rows, NTW columns, as GB swizzled 64-column blocks
-        if (!mbar_wait(gempty_bar(gb_sel), g_phase[gb_sel] ^ 1u, abort_flag, &g_tc_status, 11)) { ok = false; break; }
-        const uint32_t g_dst = s_base + L.gbuf + gb_sel * (uint32_t)(p.GB * BLK_BYTES);
-        for (int gb = 0; gb < p.GB; ++gb) {
-          const int col = n0 + gb * 64 + chunk * 8;
-          const bool col_ok = col < p.Cout && gb * 64 + chunk * 8 < p.NTW;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int64_t r = tile * TILE_R + row0 + j;
-            const bool v = col_ok && r < p.n_out;
-            cp_async_16(g_dst + gb * BLK_BYTES + doff[j], v ? gout + (size_t)r * grow_bytes + (size_t)col * 2 : gout,
-                        v ? 16u : 0u);
-          }
-        }
-        cp_async_arrive_noinc(gfull_bar(gb_sel));
-        g_phase[gb_sel] ^= 1u;
-        gb_sel ^= 1u;
-        // ---- one stage per M tile that has a valid tap in this row tile
-        int last_m = -1;
-        for (int m = 0; m < m_cnt; ++m) {
-          const int b0 = 2 * (m_lo + m), b1 = b0 + 1;
-          const bool v0 = (mask >> (b0 / p.KB)) & 1u;
-          const bool v1 = b1 < p.nblk && ((mask >> (b1 / p.KB)) & 1u);
-          if (v0 || v1) last_m = m;
-        }
-        bool first = true;
-        for (int m = 0; m <= last_m && ok; ++m) {
-          const int b0 = 2 * (m_lo + m), b1 = b0 + 1;
-          const int k0 = b0 / p.KB, k1 = b1 / p.KB;
-          const bool v0 = (mask >> k0) & 1u;
-          const bool v1 = b1 < p.nblk && ((mask >> k1) & 1u);
-          if (!(v0 || v1)) continue;
-          int rid0[4] = {-1, -1, -1, -1}, rid1[4] = {-1, -1, -1, -1};
-          if (v0) {
-            const int4 r4 = *reinterpret_cast<const int4*>(cur + k0 * TILE_R + row0);
-            rid0[0] = r4.x; rid0[1] = r4.y; rid0[2] = r4.z; rid0[3] = r4.w;
-          }
-          if (v1) {
-            const int4 r4 = *reinterpret_cast<const int4*>(cur + k1 * TILE_R + row0);
-            rid1[0] = r4.x; rid1[1] = r4.y; rid1[2] = r4.z; rid1[3] = r4.w;
-          }
+    uint32_t it = 0;
+    for (int64_t tile = t_begin; tile < t_end && ok; ++tile, ++it) {
+      const int buf = (int)(it & 1u);
+      if (!mbar_wait(ifull_bar(buf), (it >> 1) & 1u, abort_flag, &g_tc_status, 14)) { ok = false; break; }
+      const uint32_t mask = *(volatile uint32_t*)(smem + L.sidx + buf * IDX_BUF_BYTES) & group_taps;
+      const int* cur = (const int*)(smem + L.sidx + buf * IDX_BUF_BYTES + IDX_HDR_BYTES);
+      // one stage per M tile that has a valid tap in this row tile; a row tile without any
+      // still gets one (all-zero) stage, so that the grad_out buffers are handed over uniformly
+      int last_m = 0;
+      for (int m = 0; m < m_cnt; ++m) {
+        const int b0 = 2 * (m_lo + m), b1 = b0 + 1;
+        const bool v0 = (mask >> (b0 / KB)) & 1u;
+        const bool v1 = b1 < nblk && ((mask >> (b1 / KB)) & 1u);
+        if (v0 || v1) last_m = m;
+      }
+      bool first = true;
+      for (int m = 0; m <= last_m && ok; ++m) {
+        const int b0 = 2 * (m_lo + m), b1 = b0 + 1;
+        const int k0 = b0 / KB, k1 = b1 / KB;
+        const bool v0 = (mask >> k0) & 1u;
+        const bool v1 = b1 < nblk && ((mask >> k1) & 1u);
+        if (!(v0 || v1) && !(mask == 0 && m == 0)) continue;
+        const bool mine0 = owner == pw;
+        if (++owner == PROD_WARPS) owner = 0;
+        const bool mine1 = owner == pw;
+        if (++owner == PROD_WARPS) owner = 0;
+        if (mine0 || mine1) {
           if (!mbar_wait(empty_bar(s), ring_phase ^ 1u, abort_flag, &g_tc_status, 12)) { ok = false; break; }
-          const uint32_t a_dst = s_base + L.ring + s * (uint32_t)(2 * BLK_BYTES);
-          if (pt == 0) {
-            hdr[s] = (first ? 1u : 0u) | (m == last_m ? 2u : 0u) | (((touched >> m) & 1u) ? 0u : 8u) |
-                     ((uint32_t)m << 8);
-            mbar_arrive(full_bar(s));
+          const uint32_t a_dst = ring0 + s * (uint32_t)(2 * BLK_BYTES);
+          if (mine0) {
+            if (lane == 0) {
+              hdr[s] = (first ? 1u : 0u) | (m == last_m ? 2u : 0u) | (((touched >> m) & 1u) ? 0u : 8u) |
+                       ((uint32_t)m << 8);
+              mbar_arrive(full_bar(s));
+            }
+            gather_block(a_dst, v0 ? cur + k0 * TILE_R : nullptr, b0 % KB);
+          } else {
+            gather_block(a_dst + BLK_BYTES, v1 ? cur + k1 * TILE_R : nullptr, b1 < nblk ? b1 % KB : 0);
           }
-          touched |= 1u << m;
-          first = false;
-          gather_block(a_dst, rid0, b0 % p.KB);
-          gather_block(a_dst + BLK_BYTES, rid1, b1 < p.nblk ? b1 % p.KB : 0);
           cp_async_arrive_noinc(full_bar(s));
-          if (++s == S) { s = 0; ring_phase ^= 1u; }
         }
+        touched |= 1u << m;
+        first = false;
+        if (++s == NS) { s = 0; ring_phase ^= 1u; }
       }
-      if (next < t_end) {
-        buf ^= 1;
-        mask = publish_indices(buf);
+      __syncwarp();                                   // every lane has read its indices of this tile
+      if (lane == 0) mbar_arrive(iempty_bar(buf));
+    }
+    // end marker for the MMA warp: a stage without copies whose header says END
+    {
+      const bool mine0 = owner == pw;
+      if (++owner == PROD_WARPS) owner = 0;
+      const bool mine1 = owner == pw;
+      if ((mine0 || mine1) && ok && mbar_wait(empty_bar(s), ring_phase ^ 1u, abort_flag, &g_tc_status, 13)) {
+        if (mine0 && lane == 0) {
+          hdr[s] = 4u;
+          misc[18] = touched;
+          mbar_arrive(full_bar(s));
+        }
+        cp_async_arrive_noinc(full_bar(s));
       }
     }
-    // end marker for the MMA warp
-    if (ok && mbar_wait(empty_bar(s), ring_phase ^ 1u, abort_flag, &g_tc_status, 13)) {
-      if (pt == 0) {
-        hdr[s] = 4u;
-        misc[18] = touched;
-        mbar_arrive(full_bar(s));
+    cp_async_wait_all();
+  } else if (warp == LOADER_WARP) {
+    // ===================================================================== loader
+    // Per row tile: the tile-table block (one bulk copy, lane 0) and the grad_out tile
+    // (dense rows, NTW columns, as GB swizzled 64-column blocks; 8 lanes per row).
+    const uint8_t* src = (const uint8_t*)p.tiled;
+    const uint8_t* gout = (const uint8_t*)p.gout;
+    const uint32_t grow_bytes = (uint32_t)p.Cout * 2;
+    const int chunk = lane & 7, rsub = lane >> 3;
+    uint32_t it = 0;
+    for (int64_t tile = t_begin; tile < t_end; ++tile, ++it) {
+      const int b = (int)(it & 1u);
+      if (it >= 2 && !mbar_wait(iempty_bar(b), ((it >> 1) - 1u) & 1u, abort_flag, &g_tc_status, 10)) break;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(ifull_bar(b), p.tiled_block_bytes);
+        bulk_g2s(s_base + L.sidx + b * IDX_BUF_BYTES, src + (size_t)tile * p.tiled_block_bytes, p.tiled_block_bytes,
+                 ifull_bar(b));
       }
-      cp_async_arrive_noinc(full_bar(s));
+      if (!mbar_wait(gempty_bar(b), ((it >> 1) & 1u) ^ 1u, abort_flag, &g_tc_status, 11)) break;
+      const uint32_t g_dst = s_base + L.gbuf + b * (uint32_t)(p.GB * BLK_BYTES);
+      for (int gb = 0; gb < p.GB; ++gb) {
+        const int col = n0 + gb * 64 + chunk * 8;
+        const bool col_ok = col < p.Cout && gb * 64 + chunk * 8 < p.NTW;
+#pragma unroll 8
+        for (int i = 0; i < TILE_R / 4; ++i) {
+          const int r = 4 * i + rsub;
+          const int64_t grow = tile * TILE_R + r;
+          const bool v = col_ok && grow < p.n_out;
+          cp_async_16(g_dst + gb * BLK_BYTES + r * 128 + ((chunk ^ (r & 7)) << 4),
+                      v ? gout + (size_t)grow * grow_bytes + (size_t)col * 2 : gout, v ? 16u : 0u);
+        }
+      }
+      cp_async_arrive_noinc(gfull_bar(b));
     }
     cp_async_wait_all();
   } else if (warp == MMA_WARP) {
@@ -436,14 +417,19 @@ static Plan make_plan(int K, int Cin, int Cout, int64_t n_out, int dtype) {
 
 bool wgrad_tc_supported(int K, int Cin, int Cout, int dtype) { return wg::make_plan(K, Cin, Cout, 1, dtype).ok; }
 
-size_t wgrad_tc_workspace_bytes(int K, int Cin, int Cout, int64_t n_out) {
-  const wg::Plan P = wg::make_plan(K, Cin, Cout, n_out, OC_F16);
+// workspace = per-slice partials, then room for a tile table (used when the caller has none)
+static size_t wgrad_tc_partial_bytes(const wg::Plan& P, int K, int Cin, int Cout) {
   return align_up((size_t)P.slices * K * Cin * Cout * sizeof(float), 256);
 }
 
-template <bool BF16, typename I>
+size_t wgrad_tc_workspace_bytes(int K, int Cin, int Cout, int64_t n_out) {
+  const wg::Plan P = wg::make_plan(K, Cin, Cout, n_out, OC_F16);
+  return wgrad_tc_partial_bytes(P, K, Cin, Cout) + align_up(tile_table_bytes(n_out, K), 256);
+}
+
+template <bool BF16>
 static int launch_wgrad_tc_t(const wg::Params& prm, const wg::Plan& P, cudaStream_t s) {
-  auto kern = wg::wgrad_tc_kernel<BF16, I>;
+  auto kern = wg::wgrad_tc_kernel<BF16>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   OC_CUDA_OK(cudaGetDevice(&dev));
@@ -460,20 +446,26 @@ static int launch_wgrad_tc_t(const wg::Params& prm, const wg::Plan& P, cudaStrea
 int launch_wgrad_tc(const WgradArgs& a, float* grad_w, void* workspace, size_t workspace_bytes, cudaStream_t s) {
   const wg::Plan P = wg::make_plan(a.K, a.Cin, a.Cout, a.n_out, a.dtype);
   OC_REQUIRE(P.ok, OC_EINVAL, "wgrad_tc: unsupported shape");
-  const size_t need = (size_t)P.slices * a.K * a.Cin * a.Cout * sizeof(float);
+  const size_t partial_bytes = wgrad_tc_partial_bytes(P, a.K, a.Cin, a.Cout);
+  const size_t need = partial_bytes + (a.tiled ? 0 : tile_table_bytes(a.n_out, a.K));
   OC_REQUIRE(workspace && workspace_bytes >= need, OC_ENOMEM, "wgrad_tc: workspace %zu < %zu", workspace_bytes, need);
-  OC_REQUIRE(((uintptr_t)a.data % 16) == 0 && ((uintptr_t)a.grad_out % 16) == 0 && ((uintptr_t)workspace % 16) == 0,
-             OC_EINVAL, "wgrad_tc: data, grad_out and workspace must be 16-byte aligned");
+  OC_REQUIRE(((uintptr_t)a.data % 16) == 0 && ((uintptr_t)a.grad_out % 16) == 0 && ((uintptr_t)workspace % 16) == 0 &&
+                 ((uintptr_t)a.tiled % 16) == 0,
+             OC_EINVAL, "wgrad_tc: data, grad_out, tile table and workspace must be 16-byte aligned");
+  const void* tiled = a.tiled;
+  if (!tiled) {   // plain table: regroup it first (one pass over the table)
+    void* tt = (char*)workspace + partial_bytes;
+    int rc = launch_tile_table(a.table, a.idx_bytes, a.table_cols, a.taps, a.K, a.n_out, tt, s);
+    if (rc) return rc;
+    tiled = tt;
+  }
   wg::Params prm;
-  prm.data = a.data; prm.gout = a.grad_out; prm.table = a.table; prm.partial = (float*)workspace;
-  prm.n_out = a.n_out; prm.tiles_per_slice = P.tiles_per_slice; prm.table_cols = a.table_cols;
+  prm.data = a.data; prm.gout = a.grad_out; prm.tiled = tiled;
+  prm.tiled_block_bytes = (uint32_t)tile_table_block_bytes(a.K); prm.partial = (float*)workspace;
+  prm.n_out = a.n_out; prm.tiles_per_slice = P.tiles_per_slice;
   prm.K = a.K; prm.Cin = a.Cin; prm.Cout = a.Cout; prm.KB = P.KB; prm.nblk = P.nblk; prm.NTW = P.NTW;
   prm.GB = P.GB; prm.mt_per_cta = P.mt_per_cta; prm.stages = P.stages; prm.tmem_cols = P.tmem_cols;
-  prm.taps = a.taps;
-  const bool bf = a.dtype == OC_BF16;
-  int rc;
-  if (a.idx_bytes == 8) rc = bf ? launch_wgrad_tc_t<true, int64_t>(prm, P, s) : launch_wgrad_tc_t<false, int64_t>(prm, P, s);
-  else rc = bf ? launch_wgrad_tc_t<true, int32_t>(prm, P, s) : launch_wgrad_tc_t<false, int32_t>(prm, P, s);
+  int rc = a.dtype == OC_BF16 ? launch_wgrad_tc_t<true>(prm, P, s) : launch_wgrad_tc_t<false>(prm, P, s);
   if (rc) return rc;
   return reduce_partials((const float*)workspace, P.slices, (int64_t)a.K * a.Cin * a.Cout, grad_w, s);
 }

@@ -71,9 +71,10 @@ def conv_gather(data, weights, w_transposed, bias, table, taps, c_in, c_out, til
   return out
 
 
-def conv_wgrad(data, grad_out, table, taps, c_in, c_out, want_bias_grad=False):
+def conv_wgrad(data, grad_out, table, taps, c_in, c_out, want_bias_grad=False, tiles=None):
   r''' ``gw[k] = sum_r data[table[r, taps[k]]].T @ grad_out[r]`` as fp32
-  ``(K, c_in, c_out)``; optionally also ``grad_out.sum(0)``. '''
+  ``(K, c_in, c_out)``; optionally also ``grad_out.sum(0)``.  `tiles`: as in
+  :func:`conv_gather`. '''
   _lib.require_cuda(data, grad_out, table)
   data = data.contiguous()
   grad_out = grad_out.contiguous()
@@ -86,6 +87,11 @@ def conv_wgrad(data, grad_out, table, taps, c_in, c_out, want_bias_grad=False):
   gb = torch.empty(c_out, dtype=torch.float32, device=data.device) if want_bias_grad else None
   ws = _lib.workspace(_lib.lib().oc_conv_wgrad_workspace_bytes(K, c_in, c_out, n_out, dt),
                       data.device)
+  if tiles is not None and n_out > 0 and tiled_supported(K, c_in, c_out, data.dtype):
+    _lib.call('oc_conv_wgrad_tiled', _lib.ptr(data), data.shape[0], _lib.ptr(grad_out), n_out,
+              _lib.ptr(tiles), K, c_in, c_out, dt, _lib.ptr(gw), _lib.ptr(gb), _lib.ptr(ws), ws.numel(),
+              _lib.stream(data.device))
+    return gw, gb
   _lib.call('oc_conv_wgrad', _lib.ptr(data), data.shape[0], _lib.ptr(grad_out), n_out,
             _lib.ptr(table), _idx_bytes(table), table.shape[1], _lib.int_array(taps), K, c_in,
             c_out, dt, _lib.ptr(gw), _lib.ptr(gb), _lib.ptr(ws), ws.numel(),
@@ -190,7 +196,8 @@ class OctreeConvFunction(Function):
       grad_in = conv_gather(grad, weights, True, None, table_t, taps_t, cout, cin, tiles)
     if ctx.needs_input_grad[1] or (has_bias and ctx.needs_input_grad[2]):
       table, taps = octree.conv_table(depth, kernel, stride, nempty)
-      gw, gb = conv_wgrad(data, grad, table, taps, cin, cout, has_bias and ctx.needs_input_grad[2])
+      tiles = _tiles(octree, depth, kernel, stride, nempty, False, len(taps), cin, cout, data)
+      gw, gb = conv_wgrad(data, grad, table, taps, cin, cout, has_bias and ctx.needs_input_grad[2], tiles)
       grad_w = gw.to(weights.dtype) if ctx.needs_input_grad[1] else None
       grad_b = gb
     return (grad_in, grad_w, grad_b) + (None,) * 7
@@ -227,7 +234,8 @@ class OctreeDeconvFunction(Function):
       grad_in = conv_gather(grad, weights, False, None, table, taps, cout, cin, tiles)
     if ctx.needs_input_grad[1]:
       # weights are (K, out_channels, in_channels): gathered operand = grad
-      gw, _ = conv_wgrad(grad, data, table, taps, cout, cin, False)
+      tiles = _tiles(octree, nd, kernel, stride, nempty, False, len(taps), cout, cin, grad)
+      gw, _ = conv_wgrad(grad, data, table, taps, cout, cin, False, tiles)
       grad_w = gw.to(weights.dtype)
     if has_bias and ctx.needs_input_grad[2]:
       from .octree_norm import col_stats
