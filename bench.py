@@ -40,6 +40,11 @@ def workload_clouds(rank=0, batch=None, npts=NPTS):
   return pts, nrm, bid
 
 
+# dram__bytes_read + dram__bytes_write of one forward launch, per output row, from the ncu capture of
+# the 4-octree case (332.8 MB / 1 001 304 rows; traffic grows in proportion to the rows)
+DRAM_BYTES_PER_ROW = 332.4
+
+
 def peaks():
   path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
   if os.path.exists(path):
@@ -310,7 +315,7 @@ def run_ours(args):
       'ms_fwd_kernel': ms_fwd, 'build': {'mpts_per_s': build_mpts, 'points': BATCH * NPTS,
                                          'what': 'pinned host points -> octree + neighbour tables, depth 8'},
       'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': pk['tflops'], 'unit': 'TFLOP/s',
-                   'frac': achieved / pk['tflops'], 'traffic': 448.0 * n,
+                   'frac': achieved / pk['tflops'], 'traffic': DRAM_BYTES_PER_ROW * n,
                    'kernel': 'conv gather implicit GEMM (forward launch), valid-tap FLOPs', 'peak_src': pk['src']},
       'e2e': {'value': world * flops_valid / (ms_e2e * 1e-3) / 1e12, 'unit': UNIT,
               'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h, 'ms_per_step': ms_e2e},
