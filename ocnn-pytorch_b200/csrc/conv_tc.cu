@@ -88,7 +88,7 @@ struct Params {
   int KB;              // K blocks per tap
   int NT;              // output channels per CTA tile (multiple of 16, <= 256)
   int stages;
-  int tmem_cols;       // power of two >= 2 * NT
+  int tmem_cols;       // power of two >= 2 * H * NT
   TapList taps;
 };
 
@@ -96,12 +96,12 @@ struct SmemLayout {
   uint32_t stage_bytes, ring, sidx, bias, bars, hdr, misc, total;
 };
 
-__host__ __device__ inline SmemLayout smem_layout(int NT, int stages) {
+__host__ __device__ inline SmemLayout smem_layout(int NT, int stages, int H) {
   SmemLayout L;
-  L.stage_bytes = A_BYTES + NT * 128;
+  L.stage_bytes = H * A_BYTES + NT * 128;      // H gathered blocks, then the weight block
   L.ring = 0;
   L.sidx = L.ring + stages * L.stage_bytes;
-  L.bias = L.sidx + 2 * IDX_BUF_BYTES;
+  L.bias = L.sidx + 2 * H * IDX_BUF_BYTES;
   L.bars = L.bias + MAX_NT * 4;
   L.hdr = L.bars + (2 * MAX_STAGES + 9) * 8;
   L.misc = L.hdr + MAX_STAGES * 4;
@@ -128,13 +128,16 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, float ba, float bb, 
   }
 }
 
-template <bool BF16, typename I>
+// H = 128-row halves per tile (1 or 2).  With H = 2 a stage holds the gathered blocks of both
+// halves next to ONE weight block: the weight traffic from L2 (8 KB per 16 KB gathered at
+// C = 64) and the per-stage bookkeeping of the MMA warp are shared by 256 rows.
+template <bool BF16, typename I, int H>
 __global__ void __launch_bounds__(THREADS, 1)
 conv_tc_kernel(const Params p) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: swizzle atoms are 8 rows x 128 B
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const SmemLayout L = smem_layout(p.NT, p.stages);
+  const SmemLayout L = smem_layout(p.NT, p.stages, H);
   const uint32_t s_base = smem_u32(smem);
   float* sbias = (float*)(smem + L.bias);
   const uint32_t bars = pin_reg(s_base + L.bars);
@@ -148,19 +151,21 @@ conv_tc_kernel(const Params p) {
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * MAX_STAGES + a); };
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * MAX_STAGES + 2 + a); };
   const uint32_t psync_bar = bars + 8u * (2 * MAX_STAGES + 4);   // producers-only rendezvous
-  auto ifull_bar = [&](int b) { return bars + 8u * (2 * MAX_STAGES + 5 + b); };    // tile-table block b has landed
-  auto iempty_bar = [&](int b) { return bars + 8u * (2 * MAX_STAGES + 7 + b); };   // every producer warp is done with it
-  auto idx_rows = [&](int b) { return (int*)(smem + L.sidx + b * IDX_BUF_BYTES + IDX_HDR_BYTES); };
+  auto ifull_bar = [&](int b) { return bars + 8u * (2 * MAX_STAGES + 5 + b); };    // tile-table blocks of buffer b have landed
+  auto iempty_bar = [&](int b) { return bars + 8u * (2 * MAX_STAGES + 7 + b); };   // every producer warp is done with them
+  // index buffer b, half h: header word 0 = tap mask, then K rows of 128 int32
+  auto idx_hdr = [&](int b, int h) { return (volatile uint32_t*)(smem + L.sidx + (b * H + h) * IDX_BUF_BYTES); };
+  auto idx_rows = [&](int b, int h) { return (int*)(smem + L.sidx + (b * H + h) * IDX_BUF_BYTES + IDX_HDR_BYTES); };
   const bool tiled = p.tiled != nullptr;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.y * p.NT;                       // first output channel of this CTA
-  const int64_t n_tiles = (p.n_out + TILE_M - 1) / TILE_M;
+  const int64_t n_tiles = ((p.n_out + TILE_M - 1) / TILE_M + H - 1) / H;   // tiles of H x 128 rows
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(full_bar(s), 32 + 1);   // the 32 lanes of the owning warp + 1 arrive.expect_tx (weights)
-      mbar_init(empty_bar(s), 1);    // one tcgen05.commit
+      mbar_init(full_bar(s), 32 * H + 1);   // the lanes of the H owning warps + 1 arrive.expect_tx (weights)
+      mbar_init(empty_bar(s), 1);           // one tcgen05.commit
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
@@ -204,15 +209,15 @@ conv_tc_kernel(const Params p) {
     // loop bounds and strides of the stage loop, pinned in registers
     const int KB = pin_reg(p.KB), Cin = pin_reg(p.Cin), NS = pin_reg(S);
     const uint32_t ring0 = pin_reg(s_base + L.ring), stage_bytes = pin_reg(L.stage_bytes);
-    // Stages are dealt to the producer warps round-robin: a whole stage (128 rows x 8
-    // chunks of 16 B) is copied by one warp, so the per-stage bookkeeping (slot wait,
-    // header, weight copy, barrier arrival) is paid by one warp while the others work on
-    // their own stages.  8 lanes copy one 128-byte row; lane group g = lane / 8 owns the
-    // rows 32 g .. 32 g + 31 of the tile, fetched 4 indices at a time.
+    // A stage = one valid tap x one 64-channel block: H gathered blocks (128 rows x 8 chunks of
+    // 16 B each) + the weight block.  Whole blocks are dealt to the producer warps round-robin,
+    // so the per-block bookkeeping (slot wait, header, weight copy, barrier arrival) is paid by
+    // one warp while the others work on their own blocks.  8 lanes copy one 128-byte row; lane
+    // group g = lane / 8 owns the rows 32 g .. 32 g + 31 of the block, fetched 4 indices at a time.
     const int chunk = lane & 7;
     const int grp = lane >> 3;
-    const int n_own = pin_reg(S < PROD_WARPS ? S : PROD_WARPS);   // warps that own stages (a warp needs a slot of its own)
-    int owner = 0;                             // producer warp that owns the next stage
+    const int n_own = pin_reg(S * H < PROD_WARPS ? S * H : PROD_WARPS);   // warps that own blocks (a warp needs a slot of its own)
+    int owner = 0;                             // producer warp that owns the next block
     int s = 0;                                 // ring slot of the next stage
     uint32_t ring_phase = 0;                   // flips each time the ring wraps
     constexpr int NF = (OC_MAX_TAPS + FSPLIT - 1) / FSPLIT;
@@ -221,10 +226,8 @@ conv_tc_kernel(const Params p) {
     uint32_t psync_phase = 0;
     PROF_DECL;
     PROF_T(p_start);
-#ifdef OC_PROF
-    long long last_x1 = 0;
-#endif
 
+    // plain table (H == 1 only): every thread prefetches half a row of the next tile's indices
     auto fetch_indices = [&](int64_t tile) {
       const int64_t r = tile * TILE_M + frow;
 #pragma unroll
@@ -235,7 +238,7 @@ conv_tc_kernel(const Params p) {
     };
     auto publish_indices = [&](int buf) -> uint32_t {
       uint32_t m = 0;
-      int* dst = idx_rows(buf);
+      int* dst = idx_rows(buf, 0);
 #pragma unroll
       for (int i = 0; i < NF; ++i) {
         const int k = FSPLIT * i + fpart;
@@ -260,78 +263,78 @@ conv_tc_kernel(const Params p) {
     int buf = 0;
     uint32_t mask = 0;
     uint32_t it = 0;                           // tiles done by this CTA
-    if (!tiled && tile < n_tiles) {
+    if (H == 1 && !tiled && tile < n_tiles) {
       fetch_indices(tile);
       mask = publish_indices(buf);
     }
     for (; tile < n_tiles && ok; tile += gridDim.x, ++it) {
       const int64_t next = tile + gridDim.x;
       PROF_T(pf0);
-      if (tiled) {
+      if (H > 1 || tiled) {
         buf = (int)(it & 1u);
         if (!mbar_wait(ifull_bar(buf), (it >> 1) & 1u, abort_flag, &g_tc_status, 6)) { ok = false; break; }
-        mask = *(volatile uint32_t*)(smem + L.sidx + buf * IDX_BUF_BYTES);
+        mask = 0;
+#pragma unroll
+        for (int h = 0; h < H; ++h) mask |= *idx_hdr(buf, h);
       } else if (next < n_tiles) {
         fetch_indices(next);   // loads stay in flight during this tile
       }
       PROF_T(pf1); PROF_ADD(3, pf1 - pf0);
       if (mask == 0) mask = 1;                   // nothing valid: one all-zero stage keeps the flow uniform
-      const int* cur = idx_rows(buf);
       PROF_T(pl0);
       const uint32_t last_k = 31 - __clz(mask);
       const uint32_t first_k = __ffs(mask) - 1;
       for (uint32_t k = first_k; k <= last_k && ok; ++k) {
         if (!((mask >> k) & 1u)) continue;
-        for (int kb = 0; kb < KB; ++kb) {
-          PROF_T(x0);
-          const bool mine = owner == pw;            // stages are dealt round-robin
-          if (++owner == n_own) owner = 0;
-          if (mine) {
-            PROF_T(pw0); PROF_ADD(8, pw0 - x0);
-            if (!mbar_wait(empty_bar(s), ring_phase ^ 1u, abort_flag, &g_tc_status, 1)) { ok = false; break; }
-            PROF_T(pw1); PROF_ADD(0, pw1 - pw0);
-            const uint32_t a_dst = ring0 + s * stage_bytes;
-            const int kc = min(KBLK, Cin - kb * KBLK);          // channels in this block
-            if (lane == 0) {
-              if (k == first_k && kb == 0) hdr[s] = (uint32_t)__popc(mask) * (uint32_t)KB;   // stages of this tile
+        for (int kb = 0; kb < KB && ok; ++kb) {
+#pragma unroll
+          for (int h = 0; h < H; ++h) {
+            const bool mine = owner == pw;            // blocks are dealt round-robin
+            if (++owner == n_own) owner = 0;
+            if (mine) {
+              PROF_T(pw0);
+              if (!mbar_wait(empty_bar(s), ring_phase ^ 1u, abort_flag, &g_tc_status, 1)) { ok = false; break; }
+              PROF_T(pw1); PROF_ADD(0, pw1 - pw0);
+              const uint32_t a_dst = ring0 + s * stage_bytes + h * A_BYTES;
+              const int kc = min(KBLK, Cin - kb * KBLK);          // channels in this block
+              if (h == 0 && lane == 0) {
+                if (k == first_k && kb == 0) hdr[s] = (uint32_t)__popc(mask) * (uint32_t)KB;   // stages of this tile
 #ifdef OC_NOCOPY
-              mbar_arrive(full_bar(s));
+                mbar_arrive(full_bar(s));
 #else
-              mbar_arrive_expect_tx(full_bar(s), b_bytes);
-              bulk_g2s(a_dst + A_BYTES, wimg + ((size_t)k * KB + kb) * b_bytes, b_bytes, full_bar(s));
+                mbar_arrive_expect_tx(full_bar(s), b_bytes);
+                bulk_g2s(ring0 + s * stage_bytes + H * A_BYTES, wimg + ((size_t)k * KB + kb) * b_bytes, b_bytes, full_bar(s));
 #endif
-            }
+              }
 #ifndef OC_NOCOPY
-            if (chunk * 8 < kc) {
-              const uint8_t* lane_src = data + (size_t)kb * 128 + chunk * 16;
-              const int* irow = cur + k * TILE_M + grp * 32;
+              if (chunk * 8 < kc) {
+                const uint8_t* lane_src = data + (size_t)kb * 128 + chunk * 16;
+                const int* irow = idx_rows(buf, h) + k * TILE_M + grp * 32;
 #pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const int4 r4 = *reinterpret_cast<const int4*>(irow + 4 * q);
-                const int rid[4] = {r4.x, r4.y, r4.z, r4.w};
+                for (int q = 0; q < 8; ++q) {
+                  const int4 r4 = *reinterpret_cast<const int4*>(irow + 4 * q);
+                  const int rid[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const int r = grp * 32 + 4 * q + j;            // (r & 7) == (4 q + j) & 7: known at compile time
-                  const int idx = rid[j];
-                  cp_async_16(a_dst + r * 128 + ((chunk ^ ((4 * q + j) & 7)) << 4),
-                              lane_src + (size_t)(idx < 0 ? 0 : idx) * row_bytes, idx >= 0 ? 16u : 0u);
+                  for (int j = 0; j < 4; ++j) {
+                    const int r = grp * 32 + 4 * q + j;            // (r & 7) == (4 q + j) & 7: known at compile time
+                    const int idx = rid[j];
+                    cp_async_16(a_dst + r * 128 + ((chunk ^ ((4 * q + j) & 7)) << 4),
+                                lane_src + (size_t)(idx < 0 ? 0 : idx) * row_bytes, idx >= 0 ? 16u : 0u);
+                  }
                 }
               }
-            }
 #endif
-            // arrives on the stage's barrier once this lane's copies have landed; the lane
-            // itself does not wait, so every warp keeps a whole stage in flight
-            cp_async_arrive_noinc(full_bar(s));
-            PROF_T(pw2); PROF_ADD(1, pw2 - pw1); PROF_ADD(2, 1);
+              // arrives on the stage's barrier once this lane's copies have landed; the lane
+              // itself does not wait, so every warp keeps a whole block in flight
+              cp_async_arrive_noinc(full_bar(s));
+              PROF_T(pw2); PROF_ADD(1, pw2 - pw1); PROF_ADD(2, 1);
+            }
           }
           if (++s == NS) { s = 0; ring_phase ^= 1u; }
-#ifdef OC_PROF
-          { PROF_T(x1); if (!mine) PROF_ADD(7, x1 - x0); else PROF_ADD(9, x1 - x0); if (last_x1) PROF_ADD(10, x0 - last_x1); last_x1 = x1; }
-#endif
         }
       }
       PROF_T(pl1); PROF_ADD(6, pl1 - pl0);
-      if (tiled) {
+      if (H > 1 || tiled) {
         __syncwarp();                                   // every lane has read its indices of this tile
         if (lane == 0) mbar_arrive(iempty_bar(buf));
       } else if (next < n_tiles) {
@@ -346,15 +349,19 @@ conv_tc_kernel(const Params p) {
     cp_async_wait_all();   // nothing of this thread may still be writing shared memory at exit
   } else if (warp == LOADER_WARP) {
     // ===================================================================== tile-table loader
-    // One bulk copy per tile brings header + indices of the tile into one of two buffers.
+    // One bulk copy per 128-row half brings header + indices into one of two buffers.
     if (tiled && lane == 0) {
       const uint8_t* src = (const uint8_t*)p.tiled;
       uint32_t it = 0;
       for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
         const int b = (int)(it & 1u);
         if (it >= 2 && !mbar_wait(iempty_bar(b), ((it >> 1) - 1u) & 1u, abort_flag, &g_tc_status, 7)) break;
-        mbar_arrive_expect_tx(ifull_bar(b), p.tiled_block_bytes);
-        bulk_g2s(s_base + L.sidx + b * IDX_BUF_BYTES, src + (size_t)tile * p.tiled_block_bytes, p.tiled_block_bytes, ifull_bar(b));
+        // the tile table is padded to a whole number of tiles, so both halves always exist
+        mbar_arrive_expect_tx(ifull_bar(b), H * p.tiled_block_bytes);
+#pragma unroll
+        for (int h = 0; h < H; ++h)
+          bulk_g2s(s_base + L.sidx + (b * H + h) * IDX_BUF_BYTES, src + (size_t)(tile * H + h) * p.tiled_block_bytes,
+                   p.tiled_block_bytes, ifull_bar(b));
       }
     }
     __syncwarp();
@@ -364,18 +371,17 @@ conv_tc_kernel(const Params p) {
     // warp-uniform; one elected lane issues the tcgen05 instructions.
     {
       // Descriptors are formed incrementally: the low word of a descriptor holds the start
-      // address >> 4, so slot s / K step ks only add s * (stage_bytes / 16) + 2 * ks to the
-      // low word of the descriptor of slot 0.  Rebuilding the 64-bit descriptor from a
-      // run-time address for every MMA makes this loop about twice as slow.
+      // address >> 4, so slot s / half h / K step ks only add s * (stage_bytes / 16) +
+      // h * (A_BYTES / 16) + 2 * ks to the low word of the descriptor of slot 0.  Rebuilding the
+      // 64-bit descriptor from a run-time address for every MMA makes this loop about twice as slow.
       const uint32_t idesc = make_idesc(BF16 ? 1 : 0, 0, 0, TILE_M, p.NT);
       const uint64_t da0 = make_desc_sw128(s_base + L.ring, 16, 1024);
-      const uint64_t db0 = make_desc_sw128(s_base + L.ring + A_BYTES, 16, 1024);
       const uint64_t desc_hi = da0 & 0xffffffff00000000ull;
-      const uint32_t la0 = (uint32_t)da0, lb0 = (uint32_t)db0;
+      const uint32_t la0 = (uint32_t)da0;
       const uint32_t sb16 = L.stage_bytes >> 4;
-      const bool nk4 = (p.Cin & (KBLK - 1)) == 0;       // every K block is full: 4 MMAs per stage
+      const bool nk4 = (p.Cin & (KBLK - 1)) == 0;       // every K block is full: 4 MMAs per block
       int s = 0;
-      uint32_t ring_phase = 0, acc = 0, acc_phase = 0;  // acc_phase: bit a = phase of accumulator a
+      uint32_t ring_phase = 0, acc = 0, acc_phase = 0;  // acc_phase: bit a = phase of accumulator set a
       bool ok = true;
       PROF_DECL;
       PROF_T(m_start);
@@ -385,7 +391,7 @@ conv_tc_kernel(const Params p) {
         if (__any_sync(0xffffffffu, !ok)) break;
         tc_fence_after();
         PROF_T(mt1); PROF_ADD(0, mt1 - mt0);
-        const uint32_t d_tmem = tmem_base + acc * (uint32_t)p.NT;
+        const uint32_t d_tmem = tmem_base + acc * (uint32_t)(H * p.NT);
         uint32_t n_st = 1;
         int kb = 0;
         for (uint32_t st = 0; st < n_st; ++st) {
@@ -396,18 +402,23 @@ conv_tc_kernel(const Params p) {
           PROF_T(mf1); PROF_ADD(1, mf1 - mf0);
           // the first stage of a tile carries the tile's stage count
           if (st == 0) n_st = __reduce_or_sync(0xffffffffu, hdr[s]);
-          const uint32_t la = la0 + (uint32_t)s * sb16, lb = lb0 + (uint32_t)s * sb16;
+          const uint32_t la = la0 + (uint32_t)s * sb16, lb = la + H * (A_BYTES >> 4);
 #ifndef OC_NOMMA
-          if (nk4) {
 #pragma unroll
-            for (uint32_t ks = 0; ks < 4; ++ks)
-              if (elect_one())
-                umma_f16(d_tmem, desc_hi | (la + 2 * ks), desc_hi | (lb + 2 * ks), idesc, (st == 0 && ks == 0) ? 0u : 1u);
-          } else {
-            const uint32_t nk = (uint32_t)min(KBLK, p.Cin - kb * KBLK) >> 4;
-            for (uint32_t ks = 0; ks < nk; ++ks)
-              if (elect_one())
-                umma_f16(d_tmem, desc_hi | (la + 2 * ks), desc_hi | (lb + 2 * ks), idesc, (st == 0 && ks == 0) ? 0u : 1u);
+          for (int h = 0; h < H; ++h) {
+            const uint32_t lah = la + h * (A_BYTES >> 4);
+            const uint32_t dh = d_tmem + h * (uint32_t)p.NT;
+            if (nk4) {
+#pragma unroll
+              for (uint32_t ks = 0; ks < 4; ++ks)
+                if (elect_one())
+                  umma_f16(dh, desc_hi | (lah + 2 * ks), desc_hi | (lb + 2 * ks), idesc, (st == 0 && ks == 0) ? 0u : 1u);
+            } else {
+              const uint32_t nk = (uint32_t)min(KBLK, p.Cin - kb * KBLK) >> 4;
+              for (uint32_t ks = 0; ks < nk; ++ks)
+                if (elect_one())
+                  umma_f16(dh, desc_hi | (lah + 2 * ks), desc_hi | (lb + 2 * ks), idesc, (st == 0 && ks == 0) ? 0u : 1u);
+            }
           }
 #endif
           if (elect_one()) umma_commit(empty_bar(s));         // slot reusable once these MMAs have read it
@@ -416,7 +427,7 @@ conv_tc_kernel(const Params p) {
           PROF_T(mf2); PROF_ADD(2, mf2 - mf1); PROF_ADD(3, 1);
         }
         if (!ok) break;
-        if (elect_one()) umma_commit(tfull_bar(acc));         // accumulator complete
+        if (elect_one()) umma_commit(tfull_bar(acc));         // accumulators complete
         acc_phase ^= 1u << acc;
         acc ^= 1u;
       }
@@ -435,21 +446,24 @@ conv_tc_kernel(const Params p) {
       if (!mbar_wait(tfull_bar(acc), (acc_phase >> acc) & 1u, abort_flag, &g_tc_status, 4, 256)) break;
       tc_fence_after();
       PROF_T(e1); PROF_ADD(0, e1 - e0);
-      const int64_t row = tile * TILE_M + warp * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + acc * (uint32_t)p.NT;
-      for (int c0 = 0; c0 < p.NT; c0 += 16) {
-        uint32_t r[16];
-        tmem_ld16(taddr + c0, r);
-        tmem_ld_wait();
-        if (row < p.n_out && n0 + c0 < p.Cout) {
-          uint32_t o[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            o[j] = pack2<BF16>(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), sbias[c0 + 2 * j],
-                               sbias[c0 + 2 * j + 1], has_bias);
-          uint4* dst = (uint4*)(out + row * p.Cout + n0 + c0);
-          dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-          dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+      for (int h = 0; h < H; ++h) {
+        const int64_t row = (tile * H + h) * TILE_M + warp * 32 + lane;
+        const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (acc * H + h) * (uint32_t)p.NT;
+        for (int c0 = 0; c0 < p.NT; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+          if (row < p.n_out && n0 + c0 < p.Cout) {
+            uint32_t o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              o[j] = pack2<BF16>(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), sbias[c0 + 2 * j],
+                                 sbias[c0 + 2 * j + 1], has_bias);
+            uint4* dst = (uint4*)(out + row * p.Cout + n0 + c0);
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          }
         }
       }
       tc_fence_before();
@@ -507,14 +521,16 @@ __global__ void prep_weights_tc_kernel(const W* __restrict__ w, int K, int Cin, 
 }
 
 struct Plan {
-  int KB, NT, n_tiles_n, stages, tmem_cols;
+  int KB, NT, n_tiles_n, stages, tmem_cols, H;
   uint32_t smem_bytes;
   bool ok;
 };
 
-static Plan make_plan(int K, int Cin, int Cout, int dtype) {
+// H = 128-row halves per tile (see the kernel).
+static Plan make_plan(int K, int Cin, int Cout, int dtype, int H = 1) {
   Plan P = {};
   P.ok = false;
+  P.H = H;
   if (!(dtype == OC_F16 || dtype == OC_BF16)) return P;
   if (Cin < 16 || Cin % 16 != 0 || Cout < 16 || Cout % 16 != 0) return P;
   if (K < 1 || K > OC_MAX_TAPS) return P;
@@ -522,15 +538,26 @@ static Plan make_plan(int K, int Cin, int Cout, int dtype) {
   P.n_tiles_n = (Cout + MAX_NT - 1) / MAX_NT;
   P.NT = ((Cout + P.n_tiles_n - 1) / P.n_tiles_n + 15) / 16 * 16;
   P.tmem_cols = 32;
-  while (P.tmem_cols < 2 * P.NT) P.tmem_cols *= 2;
+  while (P.tmem_cols < 2 * H * P.NT) P.tmem_cols *= 2;
+  if (P.tmem_cols > 512) return P;
   const uint32_t budget = 227 * 1024 - 1024;
   int stages = MAX_STAGES;
-  while (stages > 2 && smem_layout(P.NT, stages).total > budget) --stages;
-  if (smem_layout(P.NT, stages).total > budget) return P;
+  while (stages > 2 && smem_layout(P.NT, stages, H).total > budget) --stages;
+  if (smem_layout(P.NT, stages, H).total > budget) return P;
   P.stages = stages;
-  P.smem_bytes = smem_layout(P.NT, stages).total + 1024;
+  P.smem_bytes = smem_layout(P.NT, stages, H).total + 1024;
   P.ok = true;
   return P;
+}
+
+// Two halves per tile pay when the weight block is re-fetched for many tiles and enough
+// stages still fit: tile table given, at least 4 stages, at least 4 tiles per SM.
+static Plan choose_plan(int K, int Cin, int Cout, int dtype, int64_t n_out, bool tiled) {
+  if (tiled && n_out >= (int64_t)8 * TILE_M * sm_count()) {
+    const Plan P2 = make_plan(K, Cin, Cout, dtype, 2);
+    if (P2.ok && P2.stages >= 4) return P2;
+  }
+  return make_plan(K, Cin, Cout, dtype, 1);
 }
 
 }  // namespace tc
@@ -545,7 +572,10 @@ bool conv_tc_supported(int K, int Cin, int Cout, int dtype) { return tc::make_pl
 // ---------------------------------------------------------------------------
 size_t tile_table_block_bytes(int K) { return (size_t)tc::IDX_HDR_BYTES + (size_t)K * tc::TILE_M * 4; }
 
-size_t tile_table_bytes(int64_t n_out, int K) { return (size_t)cdiv(n_out, tc::TILE_M) * tile_table_block_bytes(K); }
+// padded to an even number of blocks: the kernels may walk the table two blocks at a time
+static int64_t tile_table_blocks(int64_t n_out) { return (cdiv(n_out, tc::TILE_M) + 1) / 2 * 2; }
+
+size_t tile_table_bytes(int64_t n_out, int K) { return (size_t)tile_table_blocks(n_out) * tile_table_block_bytes(K); }
 
 template <typename I>
 __global__ void __launch_bounds__(tc::TILE_M)
@@ -573,7 +603,7 @@ tile_table_kernel(const I* __restrict__ table, int table_cols, TapList taps, int
 int launch_tile_table(const void* table, int idx_bytes, int table_cols, const TapList& taps, int K,
                       int64_t n_out, void* out, cudaStream_t s) {
   if (n_out == 0) return OC_OK;
-  const unsigned grid = (unsigned)cdiv(n_out, tc::TILE_M);
+  const unsigned grid = (unsigned)tile_table_blocks(n_out);   // a padding block holds -1 only
   const uint32_t bb = (uint32_t)tile_table_block_bytes(K);
   if (idx_bytes == 8)
     tile_table_kernel<int64_t><<<grid, tc::TILE_M, 0, s>>>((const int64_t*)table, table_cols, taps, K, n_out, (uint8_t*)out, bb);
@@ -608,9 +638,9 @@ int prep_weights_tc(const void* w, int w_dtype, int K, int Cin, int Cout, int tr
   return OC_OK;
 }
 
-template <bool BF16, typename I>
+template <bool BF16, typename I, int H>
 static int launch_conv_tc_t(const tc::Params& prm, const tc::Plan& P, cudaStream_t s) {
-  auto kern = tc::conv_tc_kernel<BF16, I>;
+  auto kern = tc::conv_tc_kernel<BF16, I, H>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   OC_CUDA_OK(cudaGetDevice(&dev));
@@ -618,7 +648,7 @@ static int launch_conv_tc_t(const tc::Params& prm, const tc::Plan& P, cudaStream
     OC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     configured_dev = dev;
   }
-  const int64_t n_tiles = cdiv(prm.n_out, tc::TILE_M);
+  const int64_t n_tiles = cdiv(cdiv(prm.n_out, tc::TILE_M), H);
   const int sms = sm_count();
   dim3 grid((unsigned)(n_tiles < sms ? n_tiles : sms), (unsigned)P.n_tiles_n);
   kern<<<grid, tc::THREADS, P.smem_bytes, s>>>(prm);
@@ -628,7 +658,7 @@ static int launch_conv_tc_t(const tc::Params& prm, const tc::Plan& P, cudaStream
 
 int launch_conv_tc(const ConvArgs& a, const void* Wimg, int* status_dev, cudaStream_t s) {
   (void)status_dev;
-  const tc::Plan P = tc::make_plan(a.K, a.Cin, a.Cout, a.dtype);
+  const tc::Plan P = tc::choose_plan(a.K, a.Cin, a.Cout, a.dtype, a.n_out, a.tiled != nullptr);
   OC_REQUIRE(P.ok, OC_EINVAL, "conv_tc: unsupported shape");
   OC_REQUIRE(((uintptr_t)a.data % 16) == 0 && ((uintptr_t)a.out % 16) == 0 && ((uintptr_t)Wimg % 16) == 0,
              OC_EINVAL, "conv_tc: data, out and workspace must be 16-byte aligned");
@@ -640,8 +670,9 @@ int launch_conv_tc(const ConvArgs& a, const void* Wimg, int* status_dev, cudaStr
   prm.n_out = a.n_out; prm.table_cols = a.table_cols; prm.K = a.K; prm.Cin = a.Cin; prm.Cout = a.Cout;
   prm.KB = P.KB; prm.NT = P.NT; prm.stages = P.stages; prm.tmem_cols = P.tmem_cols; prm.taps = a.taps;
   const bool bf = a.dtype == OC_BF16;
-  if (a.idx_bytes == 8) return bf ? launch_conv_tc_t<true, int64_t>(prm, P, s) : launch_conv_tc_t<false, int64_t>(prm, P, s);
-  return bf ? launch_conv_tc_t<true, int32_t>(prm, P, s) : launch_conv_tc_t<false, int32_t>(prm, P, s);
+  if (P.H == 2) return bf ? launch_conv_tc_t<true, int32_t, 2>(prm, P, s) : launch_conv_tc_t<false, int32_t, 2>(prm, P, s);
+  if (a.idx_bytes == 8) return bf ? launch_conv_tc_t<true, int64_t, 1>(prm, P, s) : launch_conv_tc_t<false, int64_t, 1>(prm, P, s);
+  return bf ? launch_conv_tc_t<true, int32_t, 1>(prm, P, s) : launch_conv_tc_t<false, int32_t, 1>(prm, P, s);
 }
 
 int read_tc_status(cudaStream_t s, int* h_status) {

@@ -161,6 +161,7 @@ def test_tile_table_layout_and_equivalence(mid_octree):
     assert octree.conv_tiles(d, kernel, stride, nempty, transposed) is tiles      # cached
     K, n_out = len(taps), table.shape[0]
     nt = (n_out + 127) // 128
+    nt = (nt + 1) // 2 * 2                  # padded to an even number of blocks
     blk = 16 + K * 512
     assert tiles.dtype == torch.uint8 and tiles.numel() == nt * blk
     raw = to_np(tiles).reshape(nt, blk)
@@ -186,6 +187,50 @@ def test_tile_table_layout_and_equivalence(mid_octree):
   # shapes off the tensor-core path have no tiled form: the plain table is used
   assert not b200.nn.tiled_supported(27, 30, 64, torch.float16)
   assert not b200.nn.tiled_supported(27, 64, 64, torch.float32)
+
+
+@pytest.mark.parametrize('dtype,cin,cout,n_out', [(torch.float16, 64, 64, 128 * (8 * 148 + 3) + 77),
+                                                   (torch.bfloat16, 32, 96, 128 * (8 * 148 + 2)),
+                                                   (torch.float16, 128, 128, 128 * (8 * 148 + 1) + 5)])
+def test_conv_large_random_table(dtype, cin, cout, n_out):
+  # Enough rows for the kernel to take tiles of two 128-row halves (odd and even tile counts,
+  # ragged last tile).  The table is random, so rows gather from anywhere; a fifth of the
+  # entries and whole taps of some tiles are empty.
+  g = torch.Generator(device=dev()).manual_seed(n_out + cin)
+  K, n_in = 27, 40000
+  table = torch.randint(0, n_in, (n_out, K), device=dev(), generator=g)
+  table[torch.rand(n_out, K, device=dev(), generator=g) < 0.2] = -1
+  table[1024:1024 + 256, 5] = -1                  # tap 5 empty in two tiles
+  table[4096:4096 + 128, :] = -1                  # one tile without any neighbour
+  table[4224:4224 + 128, 1:] = -1                 # its partner half only has tap 0
+  taps = list(range(K))
+  x = torch.randn(n_in, cin, device=dev(), generator=g).to(dtype)
+  w = (torch.randn(K, cin, cout, device=dev(), generator=g) / (K * cin) ** 0.5).to(dtype)
+  bias = torch.randn(cout, device=dev(), generator=g).to(dtype)
+  gy = torch.randn(n_out, cout, device=dev(), generator=g).to(dtype)
+  tiles = b200.nn.tile_table(table, taps)
+  y_plain = b200.nn.conv_gather(x, w, False, bias, table, taps, cin, cout)
+  y_tiled = b200.nn.conv_gather(x, w, False, bias, table, taps, cin, cout, tiles=tiles)
+  b200._lib.status_check(dev())
+  assert torch.equal(y_plain, y_tiled)
+  # against fp32 torch on a sample of rows (including the empty tile and the ragged end)
+  rows = torch.cat([torch.arange(0, 300, device=dev()), torch.arange(4090, 4360, device=dev()),
+                    torch.arange(n_out - 200, n_out, device=dev())])
+  t = table[rows]
+  xg = x.float()[t.clamp(min=0)] * (t >= 0).unsqueeze(-1)             # (R, K, cin)
+  ref = torch.einsum('rkc,kcd->rd', xg, w.float()).to(dtype).float() + bias.float()
+  assert_close(to_np(y_tiled[rows]), to_np(ref), TOL16, 'y')
+  # weight gradient: tile table and plain table agree bit for bit, and match fp32 torch
+  gw_plain, _ = b200.nn.conv_wgrad(x, gy, table, taps, cin, cout)
+  gw_tiled, gb = b200.nn.conv_wgrad(x, gy, table, taps, cin, cout, True, tiles=tiles)
+  b200._lib.status_check(dev())
+  assert torch.equal(gw_plain, gw_tiled)
+  ref_gw = torch.zeros(K, cin, cout, device=dev())
+  for k in range(K):
+    tk = table[:, k]
+    ref_gw[k] = (x.float()[tk.clamp(min=0)] * (tk >= 0).unsqueeze(-1)).t() @ gy.float()
+  assert_close(to_np(gw_tiled), to_np(ref_gw), 2e-3, 'gw')
+  assert_close(to_np(gb), to_np(gy.float().sum(0)), 2e-3, 'gb')
 
 
 def test_conv_is_deterministic_and_linear(mid_octree):
