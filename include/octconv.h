@@ -173,8 +173,11 @@ int oc_conv_fwd(const void* data, int64_t n_in, const void* weights, int w_dtype
  * Cin and Cout multiples of 16). */
 int oc_conv_tiled_supported(int K, int Cin, int Cout, int dtype);
 size_t oc_tile_table_bytes(int64_t n_out, int K);
+/* n_in > 0: number of feature rows the table indexes; an entry >= n_in is stored as -1 and
+ * the next oc_status_check returns OC_EINVAL (the kernels do not re-check indices).  n_in = 0: no check.
+ * The table holds an even number of blocks (a padding block of -1 if needed). */
 int oc_tile_table_build(const void* table, int idx_bytes, int table_cols, const int* h_taps, int K,
-                        int64_t n_out, void* tiles, size_t tiles_bytes, void* stream);
+                        int64_t n_out, int64_t n_in, void* tiles, size_t tiles_bytes, void* stream);
 /* oc_conv_fwd with the table given as a tile table (same K and tap order as at build). */
 int oc_conv_fwd_tiled(const void* data, int64_t n_in, const void* weights, int w_dtype,
                       int w_transposed, const void* bias, const void* tiles, int K, int64_t n_out,

@@ -87,6 +87,10 @@ extern "C" int oc_status_check(void* stream) {
   int v = 0;
   int rc = read_tc_status((cudaStream_t)stream, &v);
   if (rc) return rc;
+  OC_REQUIRE(v != 90, OC_EINVAL,
+             "a neighbour index >= n_in was met while building a tile table, or a kernel was given a tile "
+             "table built for another K; such entries were treated as -1, so results of kernels launched "
+             "since the last check are wrong");
   OC_REQUIRE(v == 0, OC_ETIMEOUT,
              "a bounded device-side wait expired in a tensor-core kernel (role code %d); results of "
              "kernels launched since the last check are invalid", v);
@@ -157,11 +161,13 @@ extern "C" size_t oc_tile_table_bytes(int64_t n_out, int K) {
 }
 
 extern "C" int oc_tile_table_build(const void* table, int idx_bytes, int table_cols, const int* h_taps,
-                                   int K, int64_t n_out, void* tiles, size_t tiles_bytes, void* stream) {
+                                   int K, int64_t n_out, int64_t n_in, void* tiles, size_t tiles_bytes,
+                                   void* stream) {
   OC_REQUIRE(K >= 1 && K <= OC_MAX_TAPS, OC_EINVAL, "oc_tile_table_build: K %d not in [1,27]", K);
   OC_REQUIRE(idx_bytes == 8 || idx_bytes == 4, OC_EINVAL, "oc_tile_table_build: idx_bytes must be 4 or 8");
   OC_REQUIRE(table_cols >= 1 && table_cols <= 27, OC_EINVAL, "oc_tile_table_build: table_cols %d not in [1,27]", table_cols);
   OC_REQUIRE(n_out >= 0 && n_out < (1LL << 31), OC_EINVAL, "oc_tile_table_build: n_out must be in [0, 2^31)");
+  OC_REQUIRE(n_in >= 0 && n_in < (1LL << 31), OC_EINVAL, "oc_tile_table_build: n_in must be in [0, 2^31)");
   TapList taps;
   int rc = make_taps(h_taps, K, table_cols, &taps, "oc_tile_table_build");
   if (rc) return rc;
@@ -170,7 +176,7 @@ extern "C" int oc_tile_table_build(const void* table, int idx_bytes, int table_c
   OC_REQUIRE(((uintptr_t)tiles % 16) == 0, OC_EINVAL, "oc_tile_table_build: tiles must be 16-byte aligned");
   OC_REQUIRE(tiles_bytes >= tile_table_bytes(n_out, K), OC_ENOMEM, "oc_tile_table_build: tiles %zu < %zu bytes",
              tiles_bytes, tile_table_bytes(n_out, K));
-  return launch_tile_table(table, idx_bytes, table_cols, taps, K, n_out, tiles, (cudaStream_t)stream);
+  return launch_tile_table(table, idx_bytes, table_cols, taps, K, n_out, n_in, tiles, (cudaStream_t)stream);
 }
 
 extern "C" int oc_conv_fwd_tiled(const void* data, int64_t n_in, const void* weights, int w_dtype,

@@ -48,7 +48,7 @@ bool conv_tc_supported(int K, int Cin, int Cout, int dtype);
 size_t tile_table_block_bytes(int K);
 size_t tile_table_bytes(int64_t n_out, int K);
 int launch_tile_table(const void* table, int idx_bytes, int table_cols, const TapList& taps, int K,
-                      int64_t n_out, void* out, cudaStream_t s);
+                      int64_t n_out, int64_t n_in, void* out, cudaStream_t s);
 size_t conv_tc_weight_bytes(int K, int Cin, int Cout);
 int prep_weights_tc(const void* w, int w_dtype, int K, int Cin, int Cout, int transposed, int dtype,
                     void* out, cudaStream_t s);

@@ -209,6 +209,7 @@ conv_tc_kernel(const Params p) {
     // loop bounds and strides of the stage loop, pinned in registers
     const int KB = pin_reg(p.KB), Cin = pin_reg(p.Cin), NS = pin_reg(S);
     const uint32_t ring0 = pin_reg(s_base + L.ring), stage_bytes = pin_reg(L.stage_bytes);
+    bool bad_index = false;                    // the tile table names taps >= K (built for another K)
     // A stage = one valid tap x one 64-channel block: H gathered blocks (128 rows x 8 chunks of
     // 16 B each) + the weight block.  Whole blocks are dealt to the producer warps round-robin,
     // so the per-block bookkeeping (slot wait, header, weight copy, barrier arrival) is paid by
@@ -276,6 +277,7 @@ conv_tc_kernel(const Params p) {
         mask = 0;
 #pragma unroll
         for (int h = 0; h < H; ++h) mask |= *idx_hdr(buf, h);
+        if (mask >> p.K) { mask &= (1u << p.K) - 1u; bad_index = true; }   // not a tile table of K taps
       } else if (next < n_tiles) {
         fetch_indices(next);   // loads stay in flight during this tile
       }
@@ -346,6 +348,7 @@ conv_tc_kernel(const Params p) {
     }
     PROF_T(p_end); PROF_ADD(5, p_end - p_start);
     PROF_FLUSH(0, 12);
+    if (bad_index) atomicMax(&g_tc_status, 90);
     cp_async_wait_all();   // nothing of this thread may still be writing shared memory at exit
   } else if (warp == LOADER_WARP) {
     // ===================================================================== tile-table loader
@@ -579,7 +582,7 @@ size_t tile_table_bytes(int64_t n_out, int K) { return (size_t)tile_table_blocks
 
 template <typename I>
 __global__ void __launch_bounds__(tc::TILE_M)
-tile_table_kernel(const I* __restrict__ table, int table_cols, TapList taps, int K, int64_t n_out,
+tile_table_kernel(const I* __restrict__ table, int table_cols, TapList taps, int K, int64_t n_out, int64_t n_in,
                   uint8_t* __restrict__ out, uint32_t block_bytes) {
   __shared__ uint32_t smask;
   if (threadIdx.x == 0) smask = 0;
@@ -590,8 +593,13 @@ tile_table_kernel(const I* __restrict__ table, int table_cols, TapList taps, int
   int* rows = (int*)(blk + tc::IDX_HDR_BYTES);
   uint32_t m = 0;
   for (int k = 0; k < K; ++k) {
-    const int v = r < n_out ? (int)table[r * table_cols + taps.t[k]] : -1;
-    rows[k * tc::TILE_M + threadIdx.x] = v < 0 ? -1 : v;
+    int64_t v64 = r < n_out ? (int64_t)table[r * table_cols + taps.t[k]] : -1;
+    if (n_in > 0 && v64 >= n_in) {   // would read past the feature rows: dropped and reported
+      v64 = -1;
+      atomicMax(&g_tc_status, 90);
+    }
+    const int v = v64 < 0 ? -1 : (int)v64;
+    rows[k * tc::TILE_M + threadIdx.x] = v;
     m |= (v >= 0 ? 1u : 0u) << k;
   }
   m = __reduce_or_sync(0xffffffffu, m);
@@ -601,14 +609,14 @@ tile_table_kernel(const I* __restrict__ table, int table_cols, TapList taps, int
 }
 
 int launch_tile_table(const void* table, int idx_bytes, int table_cols, const TapList& taps, int K,
-                      int64_t n_out, void* out, cudaStream_t s) {
+                      int64_t n_out, int64_t n_in, void* out, cudaStream_t s) {
   if (n_out == 0) return OC_OK;
   const unsigned grid = (unsigned)tile_table_blocks(n_out);   // a padding block holds -1 only
   const uint32_t bb = (uint32_t)tile_table_block_bytes(K);
   if (idx_bytes == 8)
-    tile_table_kernel<int64_t><<<grid, tc::TILE_M, 0, s>>>((const int64_t*)table, table_cols, taps, K, n_out, (uint8_t*)out, bb);
+    tile_table_kernel<int64_t><<<grid, tc::TILE_M, 0, s>>>((const int64_t*)table, table_cols, taps, K, n_out, n_in, (uint8_t*)out, bb);
   else
-    tile_table_kernel<int32_t><<<grid, tc::TILE_M, 0, s>>>((const int32_t*)table, table_cols, taps, K, n_out, (uint8_t*)out, bb);
+    tile_table_kernel<int32_t><<<grid, tc::TILE_M, 0, s>>>((const int32_t*)table, table_cols, taps, K, n_out, n_in, (uint8_t*)out, bb);
   OC_LAUNCH_OK("tile_table_kernel");
   return OC_OK;
 }

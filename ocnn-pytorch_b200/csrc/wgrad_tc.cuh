@@ -142,6 +142,7 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
     const uint8_t* data = pin_reg((const uint8_t*)p.data);
     const uint32_t row_bytes = pin_reg((uint32_t)p.Cin * 2);
     const int KB = pin_reg(p.KB), Cin = pin_reg(p.Cin), NS = pin_reg(S), nblk = pin_reg(p.nblk);
+    bool bad_index = false;        // the tile table names taps >= K (built for another K)
     const uint32_t ring0 = pin_reg(s_base + L.ring);
     const int chunk = lane & 7;
     const int grp = lane >> 3;
@@ -168,8 +169,10 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
         for (int j = 0; j < 4; ++j) {
           const int r = grp * 32 + 4 * q + j;
           const int idx = rid[j];
+#ifndef OC_NOCOPY
           cp_async_16(dst + r * 128 + ((chunk ^ ((4 * q + j) & 7)) << 4),
                       lane_src + (size_t)(idx < 0 ? 0 : idx) * row_bytes, idx >= 0 ? 16u : 0u);
+#endif
         }
       }
     };
@@ -178,7 +181,9 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
     for (int64_t tile = t_begin; tile < t_end && ok; ++tile, ++it) {
       const int buf = (int)(it & 1u);
       if (!mbar_wait(ifull_bar(buf), (it >> 1) & 1u, abort_flag, &g_tc_status, 14)) { ok = false; break; }
-      const uint32_t mask = *(volatile uint32_t*)(smem + L.sidx + buf * IDX_BUF_BYTES) & group_taps;
+      const uint32_t mask_all = *(volatile uint32_t*)(smem + L.sidx + buf * IDX_BUF_BYTES);
+      if (mask_all >> p.K) bad_index = true;            // not a tile table of K taps
+      const uint32_t mask = mask_all & group_taps;
       const int* cur = (const int*)(smem + L.sidx + buf * IDX_BUF_BYTES + IDX_HDR_BYTES);
       // one stage per M tile that has a valid tap in this row tile; a row tile without any
       // still gets one (all-zero) stage, so that the grad_out buffers are handed over uniformly
@@ -236,6 +241,7 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
         cp_async_arrive_noinc(full_bar(s));
       }
     }
+    if (bad_index) atomicMax(&g_tc_status, 90);
     cp_async_wait_all();
   } else if (warp == LOADER_WARP) {
     // ===================================================================== loader
@@ -302,8 +308,10 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
         const uint32_t d_tmem = tmem_base + m * (uint32_t)p.NTW;
 #pragma unroll
         for (uint32_t ks = 0; ks < TILE_R / 16; ++ks)
+#ifndef OC_NOMMA
           if (elect_one())
             umma_f16(d_tmem, desc_hi | (la + ks * 128), desc_hi | (lg + ks * 128), idesc, ((h & 8u) && ks == 0) ? 0u : 1u);
+#endif
         if (elect_one()) umma_commit(empty_bar(s));
         if (h & 2u) {   // last stage of the row tile: release the grad_out buffer
           if (elect_one()) umma_commit(gempty_bar(gb_sel));
@@ -455,7 +463,7 @@ int launch_wgrad_tc(const WgradArgs& a, float* grad_w, void* workspace, size_t w
   const void* tiled = a.tiled;
   if (!tiled) {   // plain table: regroup it first (one pass over the table)
     void* tt = (char*)workspace + partial_bytes;
-    int rc = launch_tile_table(a.table, a.idx_bytes, a.table_cols, a.taps, a.K, a.n_out, tt, s);
+    int rc = launch_tile_table(a.table, a.idx_bytes, a.table_cols, a.taps, a.K, a.n_out, a.n_in, tt, s);
     if (rc) return rc;
     tiled = tt;
   }

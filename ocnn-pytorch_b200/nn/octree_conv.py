@@ -27,15 +27,18 @@ def tiled_supported(K, c_in, c_out, dtype):
       bool(_lib.lib().oc_conv_tiled_supported(K, c_in, c_out, _lib.dtype_code(dtype)))
 
 
-def tile_table(table, taps):
+def tile_table(table, taps, n_in=0):
   r''' Regroups columns `taps` of a neighbour table into blocks of 128 rows (16-byte
   header with the mask of non-empty taps, then one row of 128 int32 per tap): the form
-  the tensor-core kernel fetches with one bulk copy per tile.  Returns a uint8 tensor. '''
+  the tensor-core kernel fetches with one bulk copy per tile.  Returns a uint8 tensor.
+  `n_in` > 0: the number of feature rows the table indexes; larger entries are dropped
+  and make the next ``_lib.status_check`` raise (the kernels trust the tile table). '''
   _lib.require_cuda(table)
   K, n_out = len(taps), table.shape[0]
   tiles = torch.empty(_lib.lib().oc_tile_table_bytes(n_out, K), dtype=torch.uint8, device=table.device)
   _lib.call('oc_tile_table_build', _lib.ptr(table), _idx_bytes(table), table.shape[1],
-            _lib.int_array(taps), K, n_out, _lib.ptr(tiles), tiles.numel(), _lib.stream(table.device))
+            _lib.int_array(taps), K, n_out, int(n_in), _lib.ptr(tiles), tiles.numel(),
+            _lib.stream(table.device))
   return tiles
 
 

@@ -388,7 +388,11 @@ class Octree:
     if key not in self._table_cache:
       from ..nn.octree_conv import tile_table
       table, taps = (self.conv_table_transposed if transposed else self.conv_table)(depth, kernel, stride, nempty)
-      self._table_cache[key] = tile_table(table, taps)
+      if transposed and stride == 2:     # the inverse table indexes the rows of the forward table
+        n_in = self.conv_table(depth, kernel, stride, nempty)[0].shape[0]
+      else:
+        n_in = int(self.nnum_nempty[depth] if nempty else self.nnum[depth])
+      self._table_cache[key] = tile_table(table, taps, n_in)
     return self._table_cache[key]
 
   def batch_offsets(self, depth: int, nempty: bool = False):

@@ -184,6 +184,18 @@ def test_tile_table_layout_and_equivalence(mid_octree):
       y_tiled = b200.nn.conv_gather(x, w, False, bias, table, taps, cin, cout, tiles=tiles)
       assert torch.equal(y_plain, y_tiled)
   b200._lib.status_check(dev())
+  # an index past the feature rows is dropped while the tile table is built, and reported
+  table, taps = octree.conv_table(6, '333', 1, False)
+  n_in = int(octree.nnum[6])
+  good = b200.nn.tile_table(table, taps, n_in)
+  b200._lib.status_check(dev())
+  bad = b200.nn.tile_table(table, taps, n_in - 100)
+  with pytest.raises(b200._lib.OctConvError, match='n_in'):
+    b200._lib.status_check(dev())
+  b200._lib.status_check(dev())                      # the flag is cleared by the failed check
+  kept = to_np(bad).reshape(-1, 16 + 27 * 512)[:, 16:].copy().view(np.int32)
+  full = to_np(good).reshape(-1, 16 + 27 * 512)[:, 16:].copy().view(np.int32)
+  assert np.array_equal(kept, np.where(full >= n_in - 100, -1, full))
   # shapes off the tensor-core path have no tiled form: the plain table is used
   assert not b200.nn.tiled_supported(27, 30, 64, torch.float16)
   assert not b200.nn.tiled_supported(27, 64, 64, torch.float32)
