@@ -146,9 +146,10 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
     const uint32_t ring0 = pin_reg(s_base + L.ring);
     const int chunk = lane & 7;
     const int grp = lane >> 3;
-    // taps that feed this CTA's M tiles
+    // taps that feed this CTA's M tiles; (k_lo, kb_lo) = tap and channel block of its first block
     uint32_t group_taps = 0;
     for (int b = 2 * m_lo; b < 2 * (m_lo + m_cnt) && b < nblk; ++b) group_taps |= 1u << (b / KB);
+    const int k_lo = pin_reg((2 * m_lo) / KB), kb_lo = pin_reg((2 * m_lo) % KB);
     int s = 0;
     uint32_t ring_phase = 0;
     int owner = 0;                 // producer warp that owns the next block
@@ -186,20 +187,31 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
       const uint32_t mask = mask_all & group_taps;
       const int* cur = (const int*)(smem + L.sidx + buf * IDX_BUF_BYTES + IDX_HDR_BYTES);
       // one stage per M tile that has a valid tap in this row tile; a row tile without any
-      // still gets one (all-zero) stage, so that the grad_out buffers are handed over uniformly
+      // still gets one (all-zero) stage, so that the grad_out buffers are handed over uniformly.
+      // Block b = (tap b / KB, channel block b % KB); the pair is advanced by counting, a
+      // division by the run-time KB in this loop costs as much as the copies themselves.
       int last_m = 0;
-      for (int m = 0; m < m_cnt; ++m) {
-        const int b0 = 2 * (m_lo + m), b1 = b0 + 1;
-        const bool v0 = (mask >> (b0 / KB)) & 1u;
-        const bool v1 = b1 < nblk && ((mask >> (b1 / KB)) & 1u);
-        if (v0 || v1) last_m = m;
+      {
+        int k = k_lo, kb = kb_lo;
+        for (int m = 0; m < m_cnt; ++m) {
+          const bool v0 = (mask >> k) & 1u;
+          if (++kb == KB) { kb = 0; ++k; }
+          const bool v1 = 2 * (m_lo + m) + 1 < nblk && ((mask >> k) & 1u);
+          if (++kb == KB) { kb = 0; ++k; }
+          if (v0 || v1) last_m = m;
+        }
       }
       bool first = true;
+      int k0 = k_lo, kb0 = kb_lo;
       for (int m = 0; m <= last_m && ok; ++m) {
-        const int b0 = 2 * (m_lo + m), b1 = b0 + 1;
-        const int k0 = b0 / KB, k1 = b1 / KB;
+        int k1 = k0, kb1 = kb0 + 1;               // second block of the M tile
+        if (kb1 == KB) { kb1 = 0; ++k1; }
+        const bool has1 = 2 * (m_lo + m) + 1 < nblk;
         const bool v0 = (mask >> k0) & 1u;
-        const bool v1 = b1 < nblk && ((mask >> k1) & 1u);
+        const bool v1 = has1 && ((mask >> k1) & 1u);
+        const int ck0 = k0, ckb0 = kb0;           // this M tile's first block
+        k0 = k1; kb0 = kb1 + 1;                   // first block of the next M tile
+        if (kb0 == KB) { kb0 = 0; ++k0; }
         if (!(v0 || v1) && !(mask == 0 && m == 0)) continue;
         const bool mine0 = owner == pw;
         if (++owner == PROD_WARPS) owner = 0;
@@ -214,9 +226,9 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
                        ((uint32_t)m << 8);
               mbar_arrive(full_bar(s));
             }
-            gather_block(a_dst, v0 ? cur + k0 * TILE_R : nullptr, b0 % KB);
+            gather_block(a_dst, v0 ? cur + ck0 * TILE_R : nullptr, ckb0);
           } else {
-            gather_block(a_dst + BLK_BYTES, v1 ? cur + k1 * TILE_R : nullptr, b1 < nblk ? b1 % KB : 0);
+            gather_block(a_dst + BLK_BYTES, v1 ? cur + k1 * TILE_R : nullptr, has1 ? kb1 : 0);
           }
           cp_async_arrive_noinc(full_bar(s));
         }
