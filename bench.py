@@ -532,7 +532,8 @@ def run_suite(args, b200, octree, dev):
   nn_ = [int(v) for v in o.nnum]
   passes = (3 * depth + 4 + 7) // 8
   build_bytes = P * (12 + 12 + 12) + P * 12 * 2 * passes + sum(nn_) * 12 + int(o.nnum_nempty[depth]) * 36
-  neigh_bytes = sum(nn_[1:]) * 27 * 8 + sum(nn_[:-1]) * (27 * 8 + 4)
+  # written: every table; read: the rows of the non-empty parents (nnum[d] / 8 of them) + all child pointers
+  neigh_bytes = sum(nn_[1:]) * 27 * 8 + sum(nn_[1:]) // 8 * 27 * (8 + 4) + sum(nn_[:-1]) * 4
   emit('build_octree depth10 (16 x 200k pts, device resident)', t_b, nbytes=build_bytes, mpts_per_s=round(P / t_b / 1e3, 1), nnum=nn_)
   emit('construct_all_neigh depth10', t_n, nbytes=neigh_bytes, mpts_per_s=round(P / t_n / 1e3, 1))
   emit('build + neigh depth10', t_b + t_n, nbytes=build_bytes + neigh_bytes, mpts_per_s=round(P / (t_b + t_n) / 1e3, 1))

@@ -29,43 +29,90 @@ __global__ void neigh_full_kernel(int depth, int64_t n_local, int64_t total,
   }
 }
 
-// One warp per parent node p of depth d-1.  Lanes 0..26 fetch the parent's 27
-// neighbours q and their child pointers c = children[q]; the 8 x 27 outputs of
-// the parent's octet are then assembled with shuffles:
+// One warp per NON-EMPTY parent node p of depth d-1 (most parents of a deep level are empty:
+// a block first compacts the non-empty parents of a chunk of 256 nodes with one coalesced read
+// of `children`, then its 8 warps take them in turn).  Lanes 0..26 fetch the parent's 27
+// neighbours q and their child pointers c = children[q]; the 8 x 27 outputs of the parent's
+// octet are then assembled with shuffles:
 //   t = (cx,cy,cz) + (kx,ky,kz) + 1 in [1,4]^3, parent tap = t >> 1, child = t & 1
 // (the reference's lut_parent / lut_child, octree.py:86-95).
+// Each lane writes two consecutive entries (16 bytes) per step; which parent tap / child they
+// come from depends only on the lane and the step, and is computed once per thread.
 __global__ void __launch_bounds__(256)
 neigh_from_parent_kernel(const int64_t* __restrict__ neigh_p, const int32_t* __restrict__ children_p,
                          int64_t nnum_p, int64_t* __restrict__ neigh, int32_t* __restrict__ neigh32) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  for (int64_t p = warp0; p < nnum_p; p += nwarps) {
-    const int j = children_p[p];
-    if (j < 0) continue;  // warp-uniform
-    int c = -1;
-    if (lane < 27) {
-      const int64_t q = neigh_p[p * 27 + lane];
-      if (q >= 0) c = children_p[q];
-    }
-    int64_t* out = neigh + (int64_t)j * 216;
-    int32_t* out32 = neigh32 ? neigh32 + (int64_t)j * 216 : nullptr;
+  __shared__ int s_p[256], s_j[256], s_wcnt[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // entries o = 2 (32 it + lane) and o + 1 of the octet's 216, it = 0..3
+  int kp0[4], kp1[4], ch0[4], ch1[4];
 #pragma unroll
-    for (int it = 0; it < 7; ++it) {
-      const int o = it * 32 + lane;  // 0..223, valid < 216
+  for (int it = 0; it < 4; ++it) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int o = 2 * (it * 32 + lane) + e;
       const int i = o / 27, k = o - i * 27;
       const int tx = ((i >> 2) & 1) + k / 9 + 1;
       const int ty = ((i >> 1) & 1) + (k / 3) % 3 + 1;
       const int tz = (i & 1) + k % 3 + 1;
-      const int kp = (tx >> 1) * 9 + (ty >> 1) * 3 + (tz >> 1);
+      const int kp = o < 216 ? (tx >> 1) * 9 + (ty >> 1) * 3 + (tz >> 1) : 0;
       const int ch = ((tx & 1) << 2) | ((ty & 1) << 1) | (tz & 1);
-      const int cq = __shfl_sync(0xffffffffu, c, o < 216 ? kp : 0);
-      if (o < 216) {
-        const int64_t v = cq < 0 ? -1 : (int64_t)cq * 8 + ch;
-        out[o] = v;
-        if (out32) out32[o] = (int32_t)v;
+      if (e == 0) { kp0[it] = kp; ch0[it] = ch; } else { kp1[it] = kp; ch1[it] = ch; }
+    }
+  }
+  const int64_t n_chunks = (nnum_p + 255) / 256;
+  for (int64_t chunk = blockIdx.x; chunk < n_chunks; chunk += gridDim.x) {
+    const int64_t p_mine = chunk * 256 + threadIdx.x;
+    const int j_mine = p_mine < nnum_p ? children_p[p_mine] : -1;
+    const unsigned ballot = __ballot_sync(0xffffffffu, j_mine >= 0);
+    if (lane == 0) s_wcnt[warp] = __popc(ballot);
+    __syncthreads();
+    int base = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const int c = s_wcnt[w];
+      if (w < warp) base += c;
+      total += c;
+    }
+    if (j_mine >= 0) {
+      const int pos = base + __popc(ballot & ((1u << lane) - 1u));
+      s_p[pos] = (int)threadIdx.x;
+      s_j[pos] = j_mine;
+    }
+    __syncthreads();
+    // two parents per step, so that their dependent loads overlap
+    for (int e = warp; e < total; e += 16) {
+      const bool two = e + 8 < total;
+      const int64_t pa = chunk * 256 + s_p[e], pb = chunk * 256 + s_p[two ? e + 8 : e];
+      const int ja = s_j[e], jb = s_j[two ? e + 8 : e];
+      int64_t qa = -1, qb = -1;
+      if (lane < 27) {
+        qa = neigh_p[pa * 27 + lane];
+        qb = neigh_p[pb * 27 + lane];
+      }
+      const int ca = qa >= 0 ? children_p[qa] : -1;
+      const int cb = qb >= 0 ? children_p[qb] : -1;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        if (half == 1 && !two) break;             // warp-uniform
+        const int c = half ? cb : ca;
+        const int j = half ? jb : ja;
+        longlong2* out = reinterpret_cast<longlong2*>(neigh + (int64_t)j * 216);
+        int2* out32 = neigh32 ? reinterpret_cast<int2*>(neigh32 + (int64_t)j * 216) : nullptr;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int c0 = __shfl_sync(0xffffffffu, c, kp0[it]);
+          const int c1 = __shfl_sync(0xffffffffu, c, kp1[it]);
+          const int o2 = it * 32 + lane;          // pair index, valid < 108
+          if (o2 < 108) {
+            const int64_t v0 = c0 < 0 ? -1 : (int64_t)c0 * 8 + ch0[it];
+            const int64_t v1 = c1 < 0 ? -1 : (int64_t)c1 * 8 + ch1[it];
+            out[o2] = make_longlong2(v0, v1);
+            if (out32) out32[o2] = make_int2((int)v0, (int)v1);
+          }
+        }
       }
     }
+    __syncthreads();     // the lists are rewritten by the next chunk
   }
 }
 
@@ -170,9 +217,8 @@ extern "C" int oc_neigh_from_parent(const int64_t* neigh_p, const int32_t* child
   OC_REQUIRE(nnum_p >= 0, OC_EINVAL, "oc_neigh_from_parent: negative size");
   if (nnum_p == 0) return OC_OK;
   OC_REQUIRE(neigh_p && children_p && neigh, OC_EINVAL, "oc_neigh_from_parent: null pointer");
-  const int64_t warps = nnum_p;
-  int64_t blocks = cdiv(warps, 8);
-  const int64_t cap = (int64_t)sm_count() * 32;
+  int64_t blocks = cdiv(nnum_p, 256);            // chunks of 256 parents
+  const int64_t cap = (int64_t)sm_count() * 8;   // 8 resident blocks of 256 threads per SM
   if (blocks > cap) blocks = cap;
   neigh_from_parent_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(neigh_p, children_p, nnum_p, neigh, neigh32);
   OC_LAUNCH_OK("neigh_from_parent_kernel");
