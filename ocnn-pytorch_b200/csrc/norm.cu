@@ -145,39 +145,109 @@ colstats_vec_kernel(const T* __restrict__ a, const T* __restrict__ b, int64_t n,
   }
 }
 
+// Apply kernels: a block owns the rows [r0, r1); thread (rl, v) handles the 16-byte vector v of
+// the rows r0 + rl, r0 + rl + RL, ...  The column of a thread never changes, so its per-channel
+// constants are read once into registers and the row loop is load / fma / store only (a division
+// or modulo per vector to find the column costs more than the memory traffic it accompanies).
+// Four rows are in flight per thread.
 template <typename T>
-__global__ void affine_cols_vec_kernel(const T* __restrict__ x, const float* __restrict__ scale,
-                                       const float* __restrict__ shift, int64_t nvec, int VPR, T* __restrict__ out) {
+__global__ void __launch_bounds__(CS_THREADS)
+affine_cols_vec_kernel(const T* __restrict__ x, const float* __restrict__ scale, const float* __restrict__ shift,
+                       int64_t n, int64_t rows_per_block, int C, T* __restrict__ out) {
   constexpr int N = 16 / sizeof(T);
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < nvec; t += (int64_t)gridDim.x * blockDim.x) {
-    const int c0 = (int)(t % VPR) * N;
-    float v[N];
-    load_vec<T>(x + t * N, v);
+  const int VPR = C / N;
+  const int VW = VPR < CS_THREADS ? VPR : CS_THREADS;
+  const int RL = CS_THREADS / VW;
+  const int v = threadIdx.x % VW, rl = threadIdx.x / VW;
+  if (rl >= RL) return;
+  const int64_t r0 = (int64_t)blockIdx.x * rows_per_block;
+  int64_t r1 = r0 + rows_per_block;
+  if (r1 > n) r1 = n;
+  for (int vv = v; vv < VPR; vv += VW) {
+    float sc[N], sh[N];
 #pragma unroll
-    for (int i = 0; i < N; ++i) v[i] = fmaf(v[i], scale[c0 + i], shift[c0 + i]);
-    store_vec<T>(out + t * N, v);
+    for (int i = 0; i < N; ++i) { sc[i] = scale[vv * N + i]; sh[i] = shift[vv * N + i]; }
+    const T* xp = x + (int64_t)vv * N;
+    T* op = out + (int64_t)vv * N;
+    int64_t r = r0 + rl;
+    for (; r + 3 * RL < r1; r += 4 * RL) {
+      float a[4][N];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) load_vec<T>(xp + (r + u * RL) * C, a[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) a[u][i] = fmaf(a[u][i], sc[i], sh[i]);
+        store_vec<T>(op + (r + u * RL) * C, a[u]);
+      }
+    }
+    for (; r < r1; r += RL) {
+      float a[N];
+      load_vec<T>(xp + r * C, a);
+#pragma unroll
+      for (int i = 0; i < N; ++i) a[i] = fmaf(a[i], sc[i], sh[i]);
+      store_vec<T>(op + r * C, a);
+    }
   }
 }
 
 template <typename T>
-__global__ void bn_bwd_apply_vec_kernel(const T* __restrict__ g, const T* __restrict__ x, const float* __restrict__ ka,
-                                        const float* __restrict__ kb, const float* __restrict__ kc, int64_t nvec,
-                                        int VPR, T* __restrict__ gin) {
+__global__ void __launch_bounds__(CS_THREADS)
+bn_bwd_apply_vec_kernel(const T* __restrict__ g, const T* __restrict__ x, const float* __restrict__ ka,
+                        const float* __restrict__ kb, const float* __restrict__ kc, int64_t n,
+                        int64_t rows_per_block, int C, T* __restrict__ gin) {
   constexpr int N = 16 / sizeof(T);
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < nvec; t += (int64_t)gridDim.x * blockDim.x) {
-    const int c0 = (int)(t % VPR) * N;
-    float gv[N], xv[N];
-    load_vec<T>(g + t * N, gv);
-    load_vec<T>(x + t * N, xv);
+  const int VPR = C / N;
+  const int VW = VPR < CS_THREADS ? VPR : CS_THREADS;
+  const int RL = CS_THREADS / VW;
+  const int v = threadIdx.x % VW, rl = threadIdx.x / VW;
+  if (rl >= RL) return;
+  const int64_t r0 = (int64_t)blockIdx.x * rows_per_block;
+  int64_t r1 = r0 + rows_per_block;
+  if (r1 > n) r1 = n;
+  for (int vv = v; vv < VPR; vv += VW) {
+    float a[N], b[N], c[N];
 #pragma unroll
-    for (int i = 0; i < N; ++i) gv[i] = gv[i] * ka[c0 + i] + xv[i] * kb[c0 + i] + kc[c0 + i];
-    store_vec<T>(gin + t * N, gv);
+    for (int i = 0; i < N; ++i) { a[i] = ka[vv * N + i]; b[i] = kb[vv * N + i]; c[i] = kc[vv * N + i]; }
+    const T* gp = g + (int64_t)vv * N;
+    const T* xp = x + (int64_t)vv * N;
+    T* op = gin + (int64_t)vv * N;
+    int64_t r = r0 + rl;
+    for (; r + RL < r1; r += 2 * RL) {
+      float gv[2][N], xv[2][N];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) { load_vec<T>(gp + (r + u * RL) * C, gv[u]); load_vec<T>(xp + (r + u * RL) * C, xv[u]); }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) gv[u][i] = gv[u][i] * a[i] + xv[u][i] * b[i] + c[i];
+        store_vec<T>(op + (r + u * RL) * C, gv[u]);
+      }
+    }
+    for (; r < r1; r += RL) {
+      float gv[N], xv[N];
+      load_vec<T>(gp + r * C, gv);
+      load_vec<T>(xp + r * C, xv);
+#pragma unroll
+      for (int i = 0; i < N; ++i) gv[i] = gv[i] * a[i] + xv[i] * b[i] + c[i];
+      store_vec<T>(op + r * C, gv);
+    }
   }
 }
 
 static inline bool vec16_ok(int C, int dtype, const void* p0, const void* p1, const void* p2) {
   const int N = (int)(16 / dtype_size(dtype));
   return C % N == 0 && ((uintptr_t)p0 % 16) == 0 && ((uintptr_t)p1 % 16) == 0 && ((uintptr_t)p2 % 16) == 0;
+}
+
+// blocks for an apply kernel over n rows: enough to fill the GPU, at least 64 rows each
+static inline void apply_split(int64_t n, int* blocks, int64_t* rows_per_block) {
+  int64_t nb = cdiv(n, 64);
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (nb > cap) nb = cap;
+  if (nb < 1) nb = 1;
+  *rows_per_block = cdiv(n, nb);
+  *blocks = (int)cdiv(n, *rows_per_block);
 }
 
 template <typename T>
@@ -447,38 +517,73 @@ gn_partial_vec_kernel(const T* __restrict__ x, const T* __restrict__ g, GnOffset
   }
 }
 
-// MODE 0: out = (x - mean) * inv_std * weight + bias ; MODE 1: grad_in (see gn_bwd_apply_kernel)
+// MODE 0: out = (x - mean) * inv_std * weight + bias ; MODE 1: grad_in (see gn_bwd_apply_kernel).
+// grid = (row chunks, octrees of this launch): a block works inside one octree, so the statistics
+// of a thread's channels are fixed and live in registers (same layout as the BatchNorm apply kernels).
 template <typename T, int MODE>
-__global__ void gn_apply_vec_kernel(const T* __restrict__ x, const T* __restrict__ g, GnOffsets offs, int b0, int nb,
-                                    int C, int cpg, const float* __restrict__ mean, const float* __restrict__ inv_std,
-                                    const float* __restrict__ weight, const float* __restrict__ bias,
-                                    const float* __restrict__ coef_a, const float* __restrict__ coef_b,
-                                    T* __restrict__ out) {
+__global__ void __launch_bounds__(CS_THREADS)
+gn_apply_vec_kernel(const T* __restrict__ x, const T* __restrict__ g, GnOffsets offs, int b0, int C, int cpg,
+                    const float* __restrict__ mean, const float* __restrict__ inv_std,
+                    const float* __restrict__ weight, const float* __restrict__ bias,
+                    const float* __restrict__ coef_a, const float* __restrict__ coef_b, T* __restrict__ out) {
   constexpr int N = 16 / sizeof(T);
   const int G = C / cpg;
   const int VPR = C / N;
-  const int64_t rb = offs.o[0], re = offs.o[nb];
-  for (int64_t t = rb * VPR + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < re * VPR;
-       t += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = t / VPR;
-    const int c0 = (int)(t - r * VPR) * N;
-    int lo = 0, hi = nb - 1;                    // octree of row r: offs.o[lo] <= r < offs.o[lo + 1]
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if (r >= offs.o[mid]) lo = mid; else hi = mid - 1;
-    }
-    float xv[N], gv[N], o[N];
-    load_vec<T>(x + t * N, xv);
-    if (MODE == 1) load_vec<T>(g + t * N, gv);
+  const int VW = VPR < CS_THREADS ? VPR : CS_THREADS;
+  const int RL = CS_THREADS / VW;
+  const int v = threadIdx.x % VW, rl = threadIdx.x / VW;
+  if (rl >= RL) return;
+  const int bl = blockIdx.y;
+  const int64_t rb = offs.o[bl], re = offs.o[bl + 1];
+  const int64_t rpb = (re - rb + gridDim.x - 1) / gridDim.x;
+  const int64_t r0 = rb + (int64_t)blockIdx.x * rpb;
+  int64_t r1 = r0 + rpb;
+  if (r1 > re) r1 = re;
+  for (int vv = v; vv < VPR; vv += VW) {
+    float m[N], is[N], w[N], bs[N], ca[N], cb[N];
 #pragma unroll
     for (int i = 0; i < N; ++i) {
-      const int c = c0 + i;
-      const int gi = (b0 + lo) * G + c / cpg;
-      const float y = xv[i] - mean[gi];
-      if (MODE == 0) o[i] = y * inv_std[gi] * weight[c] + bias[c];
-      else o[i] = gv[i] * weight[c] * inv_std[gi] + y * coef_a[gi] + coef_b[gi];
+      const int c = vv * N + i;
+      const int gi = (b0 + bl) * G + c / cpg;
+      m[i] = mean[gi]; is[i] = inv_std[gi]; w[i] = weight[c];
+      bs[i] = MODE == 0 ? bias[c] : 0.f;
+      ca[i] = MODE == 1 ? coef_a[gi] : 0.f;
+      cb[i] = MODE == 1 ? coef_b[gi] : 0.f;
     }
-    store_vec<T>(out + t * N, o);
+    const T* xp = x + (int64_t)vv * N;
+    const T* gp = MODE == 1 ? g + (int64_t)vv * N : nullptr;
+    T* op = out + (int64_t)vv * N;
+    int64_t r = r0 + rl;
+    for (; r + RL < r1; r += 2 * RL) {
+      float xv[2][N], gv[2][N];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        load_vec<T>(xp + (r + u * RL) * C, xv[u]);
+        if (MODE == 1) load_vec<T>(gp + (r + u * RL) * C, gv[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          const float y = xv[u][i] - m[i];
+          if (MODE == 0) xv[u][i] = y * is[i] * w[i] + bs[i];
+          else xv[u][i] = gv[u][i] * w[i] * is[i] + y * ca[i] + cb[i];
+        }
+        store_vec<T>(op + (r + u * RL) * C, xv[u]);
+      }
+    }
+    for (; r < r1; r += RL) {
+      float xv[N], gv[N];
+      load_vec<T>(xp + r * C, xv);
+      if (MODE == 1) load_vec<T>(gp + r * C, gv);
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        const float y = xv[i] - m[i];
+        if (MODE == 0) xv[i] = y * is[i] * w[i] + bs[i];
+        else xv[i] = gv[i] * w[i] * is[i] + y * ca[i] + cb[i];
+      }
+      store_vec<T>(op + r * C, xv);
+    }
   }
 }
 
@@ -534,6 +639,14 @@ static void gn_partials(const void* x, const void* g, const int64_t* h_offsets, 
     gn_partial_kernel<T, MODE><<<grid, CS_THREADS, 0, s>>>((const T*)x, (const T*)g, o, b0, C, cpg, CT, mean,
                                                            inv_std, weight, p1, p2);
   }
+}
+
+// row chunks per octree for the apply kernels: fill the GPU, at least 64 rows per chunk on average
+static inline int gn_apply_chunks(int64_t rows, int nb) {
+  int64_t per = cdiv(cdiv(rows, nb > 0 ? nb : 1), 64);
+  const int64_t cap = cdiv((int64_t)sm_count() * 16, nb > 0 ? nb : 1);
+  if (per > cap) per = cap;
+  return (int)(per < 1 ? 1 : per);
 }
 
 static void gn_finalize(const float* p1, const float* p2, const int64_t* h_offsets, int batch, int C, int cpg,
@@ -649,12 +762,11 @@ extern "C" int oc_affine_cols(const void* x, const float* scale, const float* sh
   const int64_t total = n * C;
   const unsigned g = grid_1d(total, 256, 32);
   if (vec16_ok(C, dtype, x, out, nullptr)) {
-    const int N = (int)(16 / dtype_size(dtype));
-    const int64_t nvec = total / N;
-    const unsigned gv = grid_1d(nvec, 256, 32);
-    if (dtype == OC_F32) affine_cols_vec_kernel<float><<<gv, 256, 0, s>>>((const float*)x, scale, shift, nvec, C / N, (float*)out);
-    else if (dtype == OC_F16) affine_cols_vec_kernel<__half><<<gv, 256, 0, s>>>((const __half*)x, scale, shift, nvec, C / N, (__half*)out);
-    else affine_cols_vec_kernel<__nv_bfloat16><<<gv, 256, 0, s>>>((const __nv_bfloat16*)x, scale, shift, nvec, C / N, (__nv_bfloat16*)out);
+    int gv; int64_t rpb;
+    apply_split(n, &gv, &rpb);
+    if (dtype == OC_F32) affine_cols_vec_kernel<float><<<gv, CS_THREADS, 0, s>>>((const float*)x, scale, shift, n, rpb, C, (float*)out);
+    else if (dtype == OC_F16) affine_cols_vec_kernel<__half><<<gv, CS_THREADS, 0, s>>>((const __half*)x, scale, shift, n, rpb, C, (__half*)out);
+    else affine_cols_vec_kernel<__nv_bfloat16><<<gv, CS_THREADS, 0, s>>>((const __nv_bfloat16*)x, scale, shift, n, rpb, C, (__nv_bfloat16*)out);
   } else
   if (dtype == OC_F32) affine_cols_kernel<float><<<g, 256, 0, s>>>((const float*)x, scale, shift, total, C, (float*)out);
   else if (dtype == OC_F16) affine_cols_kernel<__half><<<g, 256, 0, s>>>((const __half*)x, scale, shift, total, C, (__half*)out);
@@ -673,12 +785,11 @@ extern "C" int oc_bn_bwd_apply(const void* g, const void* x, const float* ka, co
   const int64_t total = n * C;
   const unsigned gr = grid_1d(total, 256, 32);
   if (vec16_ok(C, dtype, g, x, grad_in)) {
-    const int N = (int)(16 / dtype_size(dtype));
-    const int64_t nvec = total / N;
-    const unsigned gv = grid_1d(nvec, 256, 32);
-    if (dtype == OC_F32) bn_bwd_apply_vec_kernel<float><<<gv, 256, 0, s>>>((const float*)g, (const float*)x, ka, kb, kc, nvec, C / N, (float*)grad_in);
-    else if (dtype == OC_F16) bn_bwd_apply_vec_kernel<__half><<<gv, 256, 0, s>>>((const __half*)g, (const __half*)x, ka, kb, kc, nvec, C / N, (__half*)grad_in);
-    else bn_bwd_apply_vec_kernel<__nv_bfloat16><<<gv, 256, 0, s>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)x, ka, kb, kc, nvec, C / N, (__nv_bfloat16*)grad_in);
+    int gv; int64_t rpb;
+    apply_split(n, &gv, &rpb);
+    if (dtype == OC_F32) bn_bwd_apply_vec_kernel<float><<<gv, CS_THREADS, 0, s>>>((const float*)g, (const float*)x, ka, kb, kc, n, rpb, C, (float*)grad_in);
+    else if (dtype == OC_F16) bn_bwd_apply_vec_kernel<__half><<<gv, CS_THREADS, 0, s>>>((const __half*)g, (const __half*)x, ka, kb, kc, n, rpb, C, (__half*)grad_in);
+    else bn_bwd_apply_vec_kernel<__nv_bfloat16><<<gv, CS_THREADS, 0, s>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)x, ka, kb, kc, n, rpb, C, (__nv_bfloat16*)grad_in);
   } else
   if (dtype == OC_F32) bn_bwd_apply_kernel<float><<<gr, 256, 0, s>>>((const float*)g, (const float*)x, ka, kb, kc, total, C, (float*)grad_in);
   else if (dtype == OC_F16) bn_bwd_apply_kernel<__half><<<gr, 256, 0, s>>>((const __half*)g, (const __half*)x, ka, kb, kc, total, C, (__half*)grad_in);
@@ -733,8 +844,8 @@ extern "C" int oc_gn_fwd(const void* x, const int64_t* h_offsets, int batch, int
     const int64_t total = (o.o[nb] - o.o[0]) * C;
     if (total == 0) continue;
     if (vec16_ok(C, dtype, x, out, nullptr)) {
-      const int N = (int)(16 / dtype_size(dtype));
-      GN_T(dtype, (gn_apply_vec_kernel<T, 0><<<grid_1d(total / N, 256, 32), 256, 0, s>>>((const T*)x, nullptr, o, b0, nb, C, cpg, mean, inv_std, weight, bias, nullptr, nullptr, (T*)out)));
+      const dim3 ga((unsigned)gn_apply_chunks(o.o[nb] - o.o[0], nb), (unsigned)nb);
+      GN_T(dtype, (gn_apply_vec_kernel<T, 0><<<ga, CS_THREADS, 0, s>>>((const T*)x, nullptr, o, b0, C, cpg, mean, inv_std, weight, bias, nullptr, nullptr, (T*)out)));
     } else
     GN_T(dtype, (gn_apply_kernel<T><<<grid_1d(total, 256, 32), 256, 0, s>>>((const T*)x, o, b0, nb, C, cpg, mean, inv_std, weight, bias, (T*)out)));
   }
@@ -770,8 +881,8 @@ extern "C" int oc_gn_bwd(const void* grad_out, const void* x, const int64_t* h_o
       const int64_t total = (o.o[nb] - o.o[0]) * C;
       if (total == 0) continue;
       if (vec16_ok(C, dtype, x, grad_out, grad_in)) {
-        const int N = (int)(16 / dtype_size(dtype));
-        GN_T(dtype, (gn_apply_vec_kernel<T, 1><<<grid_1d(total / N, 256, 32), 256, 0, s>>>((const T*)x, (const T*)grad_out, o, b0, nb, C, cpg, mean, inv_std, weight, nullptr, P.coef_a, P.coef_b, (T*)grad_in)));
+        const dim3 ga((unsigned)gn_apply_chunks(o.o[nb] - o.o[0], nb), (unsigned)nb);
+        GN_T(dtype, (gn_apply_vec_kernel<T, 1><<<ga, CS_THREADS, 0, s>>>((const T*)x, (const T*)grad_out, o, b0, C, cpg, mean, inv_std, weight, nullptr, P.coef_a, P.coef_b, (T*)grad_in)));
       } else
       GN_T(dtype, (gn_bwd_apply_kernel<T><<<grid_1d(total, 256, 32), 256, 0, s>>>((const T*)grad_out, (const T*)x, o, b0, nb, C, cpg, mean, inv_std, weight, P.coef_a, P.coef_b, (T*)grad_in)));
     }
