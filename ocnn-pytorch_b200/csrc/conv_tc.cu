@@ -85,7 +85,9 @@ struct Params {
   int64_t n_out;
   int table_cols;
   int K, Cin, Cout;
-  int KB;              // K blocks per tap
+  int KB;              // 64-channel blocks per tap (1 when Cin <= 64)
+  int PACK;            // taps per block: 64 / Cin when Cin is 16 or 32, else 1
+  int NBLK;            // blocks of the reduction = weight blocks per N tile
   int NT;              // output channels per CTA tile (multiple of 16, <= 256)
   int stages;
   int tmem_cols;       // power of two >= 2 * H * NT
@@ -204,10 +206,11 @@ conv_tc_kernel(const Params p) {
     const I* table = (const I*)p.table;
     const uint8_t* data = pin_reg((const uint8_t*)p.data);
     const uint32_t row_bytes = pin_reg((uint32_t)p.Cin * 2);
-    const uint8_t* wimg = pin_reg((const uint8_t*)p.wimg + (size_t)blockIdx.y * p.K * p.KB * (size_t)(p.NT * 128));
+    const uint8_t* wimg = pin_reg((const uint8_t*)p.wimg + (size_t)blockIdx.y * p.NBLK * (size_t)(p.NT * 128));
     const uint32_t b_bytes = pin_reg((uint32_t)p.NT * 128);
     // loop bounds and strides of the stage loop, pinned in registers
-    const int KB = pin_reg(p.KB), Cin = pin_reg(p.Cin), NS = pin_reg(S);
+    const int KB = pin_reg(p.KB), Cin = pin_reg(p.Cin), NS = pin_reg(S), PACK = pin_reg(p.PACK), K = pin_reg(p.K);
+    const uint32_t pmask = (1u << PACK) - 1u;      // tap bits of one block
     const uint32_t ring0 = pin_reg(s_base + L.ring), stage_bytes = pin_reg(L.stage_bytes);
     bool bad_index = false;                    // the tile table names taps >= K (built for another K)
     // A stage = one valid tap x one 64-channel block: H gathered blocks (128 rows x 8 chunks of
@@ -217,6 +220,11 @@ conv_tc_kernel(const Params p) {
     // group g = lane / 8 owns the rows 32 g .. 32 g + 31 of the block, fetched 4 indices at a time.
     const int chunk = lane & 7;
     const int grp = lane >> 3;
+    // Cin = 16 / 32: a 128-byte row holds 4 / 2 taps; this lane's 16-byte chunk belongs to tap
+    // (first tap of the block) + sub and to bytes ch_off.. of that tap's row.  Otherwise one tap.
+    const int cpt = PACK > 1 ? Cin >> 3 : 8;       // chunks per tap
+    const int sub = PACK > 1 ? chunk / cpt : 0;
+    const int ch_off = (PACK > 1 ? chunk % cpt : chunk) * 16;
     const int n_own = pin_reg(S * H < PROD_WARPS ? S * H : PROD_WARPS);   // warps that own blocks (a warp needs a slot of its own)
     int owner = 0;                             // producer warp that owns the next block
     int s = 0;                                 // ring slot of the next stage
@@ -284,11 +292,21 @@ conv_tc_kernel(const Params p) {
       PROF_T(pf1); PROF_ADD(3, pf1 - pf0);
       if (mask == 0) mask = 1;                   // nothing valid: one all-zero stage keeps the flow uniform
       PROF_T(pl0);
-      const uint32_t last_k = 31 - __clz(mask);
-      const uint32_t first_k = __ffs(mask) - 1;
-      for (uint32_t k = first_k; k <= last_k && ok; ++k) {
-        if (!((mask >> k) & 1u)) continue;
-        for (int kb = 0; kb < KB && ok; ++kb) {
+      // Candidate blocks in order: (tap k .. k + PACK - 1, channel block kb); candidate number cb
+      // is also the block's place in the weight image.  A block is a stage if one of its taps
+      // has a valid row in this tile.
+      uint32_t n_st = (uint32_t)__popc(mask) * (uint32_t)KB;
+      if (PACK > 1) {
+        n_st = 0;
+        for (int k = 0; k < K; k += PACK) n_st += ((mask >> k) & pmask) ? 1u : 0u;
+      }
+      bool first = true;
+      int k = 0, kb = 0;
+      for (int cb = 0; k < K && ok; ++cb) {
+        const int k_blk = k, kb_blk = kb;
+        if (++kb == KB) { kb = 0; k += PACK; }
+        if (!((mask >> k_blk) & pmask)) continue;
+        {
 #pragma unroll
           for (int h = 0; h < H; ++h) {
             const bool mine = owner == pw;            // blocks are dealt round-robin
@@ -298,20 +316,21 @@ conv_tc_kernel(const Params p) {
               if (!mbar_wait(empty_bar(s), ring_phase ^ 1u, abort_flag, &g_tc_status, 1)) { ok = false; break; }
               PROF_T(pw1); PROF_ADD(0, pw1 - pw0);
               const uint32_t a_dst = ring0 + s * stage_bytes + h * A_BYTES;
-              const int kc = min(KBLK, Cin - kb * KBLK);          // channels in this block
               if (h == 0 && lane == 0) {
-                if (k == first_k && kb == 0) hdr[s] = (uint32_t)__popc(mask) * (uint32_t)KB;   // stages of this tile
+                if (first) hdr[s] = n_st;               // the first stage of a tile carries its stage count
 #ifdef OC_NOCOPY
                 mbar_arrive(full_bar(s));
 #else
                 mbar_arrive_expect_tx(full_bar(s), b_bytes);
-                bulk_g2s(ring0 + s * stage_bytes + H * A_BYTES, wimg + ((size_t)k * KB + kb) * b_bytes, b_bytes, full_bar(s));
+                bulk_g2s(ring0 + s * stage_bytes + H * A_BYTES, wimg + (size_t)cb * b_bytes, b_bytes, full_bar(s));
 #endif
               }
 #ifndef OC_NOCOPY
-              if (chunk * 8 < kc) {
-                const uint8_t* lane_src = data + (size_t)kb * 128 + chunk * 16;
-                const int* irow = idx_rows(buf, h) + k * TILE_M + grp * 32;
+              const int k_lane = k_blk + sub;            // this lane's tap
+              const bool live = PACK > 1 ? k_lane < K : chunk * 8 < min(KBLK, Cin - kb_blk * KBLK);
+              {
+                const uint8_t* lane_src = data + (size_t)kb_blk * 128 + ch_off;
+                const int* irow = idx_rows(buf, h) + (live ? k_lane : 0) * TILE_M + grp * 32;
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
                   const int4 r4 = *reinterpret_cast<const int4*>(irow + 4 * q);
@@ -319,7 +338,7 @@ conv_tc_kernel(const Params p) {
 #pragma unroll
                   for (int j = 0; j < 4; ++j) {
                     const int r = grp * 32 + 4 * q + j;            // (r & 7) == (4 q + j) & 7: known at compile time
-                    const int idx = rid[j];
+                    const int idx = live ? rid[j] : -1;            // dead chunk (past Cin or past the last tap): zeros
                     cp_async_16(a_dst + r * 128 + ((chunk ^ ((4 * q + j) & 7)) << 4),
                                 lane_src + (size_t)(idx < 0 ? 0 : idx) * row_bytes, idx >= 0 ? 16u : 0u);
                   }
@@ -332,6 +351,7 @@ conv_tc_kernel(const Params p) {
               PROF_T(pw2); PROF_ADD(1, pw2 - pw1); PROF_ADD(2, 1);
             }
           }
+          first = false;
           if (++s == NS) { s = 0; ring_phase ^= 1u; }
         }
       }
@@ -382,7 +402,7 @@ conv_tc_kernel(const Params p) {
       const uint64_t desc_hi = da0 & 0xffffffff00000000ull;
       const uint32_t la0 = (uint32_t)da0;
       const uint32_t sb16 = L.stage_bytes >> 4;
-      const bool nk4 = (p.Cin & (KBLK - 1)) == 0;       // every K block is full: 4 MMAs per block
+      const bool nk4 = p.PACK > 1 || (p.Cin & (KBLK - 1)) == 0;   // every K block is full (or zero-padded): 4 MMAs per block
       int s = 0;
       uint32_t ring_phase = 0, acc = 0, acc_phase = 0;  // acc_phase: bit a = phase of accumulator set a
       bool ok = true;
@@ -500,21 +520,22 @@ conv_tc_kernel(const Params p) {
 // ---------------------------------------------------------------------------
 template <typename W, bool BF16>
 __global__ void prep_weights_tc_kernel(const W* __restrict__ w, int K, int Cin, int Cout, int transposed,
-                                       int KB, int NT, int n_tiles_n, uint16_t* __restrict__ img) {
-  const int64_t total = (int64_t)n_tiles_n * K * KB * NT * 64;
+                                       int KB, int PACK, int NBLK, int NT, int n_tiles_n, uint16_t* __restrict__ img) {
+  const int64_t total = (int64_t)n_tiles_n * NBLK * NT * 64;
   for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total;
        t += (int64_t)gridDim.x * blockDim.x) {
-    const int e = (int)(t % 64);
+    const int e = (int)(t % 64);                  // element of the 64-wide reduction block
     const int row = (int)((t / 64) % NT);
     const int64_t blk = t / (64 * (int64_t)NT);
-    const int kb = (int)(blk % KB);
-    const int k = (int)((blk / KB) % K);
-    const int nt = (int)(blk / ((int64_t)KB * K));
+    const int cb = (int)(blk % NBLK);             // block within the N tile
+    const int nt = (int)(blk / NBLK);
+    int k, ci;
+    if (PACK > 1) { k = cb * PACK + e / Cin; ci = e % Cin; }      // several taps per block
+    else { k = cb / KB; ci = (cb % KB) * 64 + e; }
     const int chunk = e >> 3, within = e & 7;
-    const int ci = kb * 64 + chunk * 8 + within;
     const int co = nt * NT + row;
     float v = 0.f;
-    if (ci < Cin && co < Cout) {
+    if (k < K && ci < Cin && co < Cout) {
       const int64_t src = transposed ? ((int64_t)k * Cout + co) * Cin + ci : ((int64_t)k * Cin + ci) * Cout + co;
       v = to_f32<W>(w[src]);
     }
@@ -524,7 +545,7 @@ __global__ void prep_weights_tc_kernel(const W* __restrict__ w, int K, int Cin, 
 }
 
 struct Plan {
-  int KB, NT, n_tiles_n, stages, tmem_cols, H;
+  int KB, PACK, NBLK, NT, n_tiles_n, stages, tmem_cols, H;
   uint32_t smem_bytes;
   bool ok;
 };
@@ -538,6 +559,8 @@ static Plan make_plan(int K, int Cin, int Cout, int dtype, int H = 1) {
   if (Cin < 16 || Cin % 16 != 0 || Cout < 16 || Cout % 16 != 0) return P;
   if (K < 1 || K > OC_MAX_TAPS) return P;
   P.KB = (Cin + KBLK - 1) / KBLK;
+  P.PACK = (Cin == 16 || Cin == 32) ? KBLK / Cin : 1;     // taps that share one 64-wide block
+  P.NBLK = P.PACK > 1 ? (K + P.PACK - 1) / P.PACK : K * P.KB;
   P.n_tiles_n = (Cout + MAX_NT - 1) / MAX_NT;
   P.NT = ((Cout + P.n_tiles_n - 1) / P.n_tiles_n + 15) / 16 * 16;
   P.tmem_cols = 32;
@@ -623,24 +646,24 @@ int launch_tile_table(const void* table, int idx_bytes, int table_cols, const Ta
 
 size_t conv_tc_weight_bytes(int K, int Cin, int Cout) {
   const tc::Plan P = tc::make_plan(K, Cin, Cout, OC_F16);
-  return (size_t)P.n_tiles_n * K * P.KB * P.NT * 128;
+  return (size_t)P.n_tiles_n * P.NBLK * P.NT * 128;
 }
 
 int prep_weights_tc(const void* w, int w_dtype, int K, int Cin, int Cout, int transposed, int dtype,
                     void* out, cudaStream_t s) {
   const tc::Plan P = tc::make_plan(K, Cin, Cout, dtype);
   OC_REQUIRE(P.ok, OC_EINVAL, "conv_tc: unsupported shape");
-  const int64_t total = (int64_t)P.n_tiles_n * K * P.KB * P.NT * 64;
+  const int64_t total = (int64_t)P.n_tiles_n * P.NBLK * P.NT * 64;
   const unsigned g = grid_1d(total, 256, 8);
   uint16_t* img = (uint16_t*)out;
   const bool bf = dtype == OC_BF16;
   if (w_dtype == OC_F32) {
-    if (bf) tc::prep_weights_tc_kernel<float, true><<<g, 256, 0, s>>>((const float*)w, K, Cin, Cout, transposed, P.KB, P.NT, P.n_tiles_n, img);
-    else tc::prep_weights_tc_kernel<float, false><<<g, 256, 0, s>>>((const float*)w, K, Cin, Cout, transposed, P.KB, P.NT, P.n_tiles_n, img);
+    if (bf) tc::prep_weights_tc_kernel<float, true><<<g, 256, 0, s>>>((const float*)w, K, Cin, Cout, transposed, P.KB, P.PACK, P.NBLK, P.NT, P.n_tiles_n, img);
+    else tc::prep_weights_tc_kernel<float, false><<<g, 256, 0, s>>>((const float*)w, K, Cin, Cout, transposed, P.KB, P.PACK, P.NBLK, P.NT, P.n_tiles_n, img);
   } else if (bf) {
-    tc::prep_weights_tc_kernel<__nv_bfloat16, true><<<g, 256, 0, s>>>((const __nv_bfloat16*)w, K, Cin, Cout, transposed, P.KB, P.NT, P.n_tiles_n, img);
+    tc::prep_weights_tc_kernel<__nv_bfloat16, true><<<g, 256, 0, s>>>((const __nv_bfloat16*)w, K, Cin, Cout, transposed, P.KB, P.PACK, P.NBLK, P.NT, P.n_tiles_n, img);
   } else {
-    tc::prep_weights_tc_kernel<__half, false><<<g, 256, 0, s>>>((const __half*)w, K, Cin, Cout, transposed, P.KB, P.NT, P.n_tiles_n, img);
+    tc::prep_weights_tc_kernel<__half, false><<<g, 256, 0, s>>>((const __half*)w, K, Cin, Cout, transposed, P.KB, P.PACK, P.NBLK, P.NT, P.n_tiles_n, img);
   }
   OC_LAUNCH_OK("prep_weights_tc_kernel");
   return OC_OK;
@@ -676,7 +699,7 @@ int launch_conv_tc(const ConvArgs& a, const void* Wimg, int* status_dev, cudaStr
   prm.tiled = a.tiled; prm.tiled_block_bytes = (uint32_t)tile_table_block_bytes(a.K);
   OC_REQUIRE(((uintptr_t)a.tiled % 16) == 0, OC_EINVAL, "conv_tc: the tile table must be 16-byte aligned");
   prm.n_out = a.n_out; prm.table_cols = a.table_cols; prm.K = a.K; prm.Cin = a.Cin; prm.Cout = a.Cout;
-  prm.KB = P.KB; prm.NT = P.NT; prm.stages = P.stages; prm.tmem_cols = P.tmem_cols; prm.taps = a.taps;
+  prm.KB = P.KB; prm.PACK = P.PACK; prm.NBLK = P.NBLK; prm.NT = P.NT; prm.stages = P.stages; prm.tmem_cols = P.tmem_cols; prm.taps = a.taps;
   const bool bf = a.dtype == OC_BF16;
   if (P.H == 2) return bf ? launch_conv_tc_t<true, int32_t, 2>(prm, P, s) : launch_conv_tc_t<false, int32_t, 2>(prm, P, s);
   if (a.idx_bytes == 8) return bf ? launch_conv_tc_t<true, int64_t, 1>(prm, P, s) : launch_conv_tc_t<false, int64_t, 1>(prm, P, s);
