@@ -55,8 +55,9 @@ struct Params {
   int64_t n_out;
   int64_t tiles_per_slice;
   int K, Cin, Cout;
-  int KB;               // 64-channel blocks per tap
-  int nblk;             // K * KB
+  int KB;               // 64-channel blocks per tap (1 when Cin <= 64)
+  int PACK;             // taps per block: 64 / Cin when Cin is 16 or 32, else 1
+  int nblk;             // blocks of the M extent: K * KB, or ceil(K / PACK)
   int NTW;              // output channels per CTA (multiple of 16, <= 128)
   int GB;               // 64-column blocks of grad_out per tile = ceil(NTW / 64)
   int mt_per_cta;
@@ -142,29 +143,46 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
     const uint8_t* data = pin_reg((const uint8_t*)p.data);
     const uint32_t row_bytes = pin_reg((uint32_t)p.Cin * 2);
     const int KB = pin_reg(p.KB), Cin = pin_reg(p.Cin), NS = pin_reg(S), nblk = pin_reg(p.nblk);
+    const int PACK = pin_reg(p.PACK), K = pin_reg(p.K);
+    const uint32_t pmask = (1u << PACK) - 1u;      // tap bits of one block
     bool bad_index = false;        // the tile table names taps >= K (built for another K)
     const uint32_t ring0 = pin_reg(s_base + L.ring);
     const int chunk = lane & 7;
     const int grp = lane >> 3;
-    // taps that feed this CTA's M tiles; (k_lo, kb_lo) = tap and channel block of its first block
+    // Cin = 16 / 32: a 128-byte row holds 4 / 2 taps; this lane's 16-byte chunk belongs to tap
+    // (first tap of the block) + sub and to bytes ch_off.. of that tap's row.  Otherwise one tap.
+    const int cpt = PACK > 1 ? Cin >> 3 : 8;       // chunks per tap
+    const int sub = PACK > 1 ? chunk / cpt : 0;
+    const int ch_off = (PACK > 1 ? chunk % cpt : chunk) * 16;
+    // block b = (first tap, channel block): (b / KB, b % KB), or (b * PACK, 0) when taps are packed;
+    // (k_lo, kb_lo) = that of this CTA's first block; group_taps = taps that feed its M tiles
+    const int k_lo = pin_reg(PACK > 1 ? 2 * m_lo * PACK : (2 * m_lo) / KB);
+    const int kb_lo = pin_reg(PACK > 1 ? 0 : (2 * m_lo) % KB);
     uint32_t group_taps = 0;
-    for (int b = 2 * m_lo; b < 2 * (m_lo + m_cnt) && b < nblk; ++b) group_taps |= 1u << (b / KB);
-    const int k_lo = pin_reg((2 * m_lo) / KB), kb_lo = pin_reg((2 * m_lo) % KB);
+    {
+      int k = k_lo, kb = kb_lo;
+      for (int b = 2 * m_lo; b < 2 * (m_lo + m_cnt) && b < nblk; ++b) {
+        group_taps |= pmask << k;
+        if (++kb == KB) { kb = 0; k += PACK; }
+      }
+    }
     int s = 0;
     uint32_t ring_phase = 0;
     int owner = 0;                 // producer warp that owns the next block
     bool ok = true;
     uint32_t touched = 0;
 
-    // Copies one 64-channel block (128 rows) of tap row `irow` (null: no valid row, zeros):
-    // 8 lanes copy one 128-byte row; lane group `grp` owns rows 32 grp .. 32 grp + 31.
-    auto gather_block = [&](uint32_t dst, const int* irow, int kb) {
-      const bool live = chunk * 8 < min(64, Cin - kb * 64);   // channels past Cin: zeros
-      const uint8_t* lane_src = data + (size_t)kb * 128 + chunk * 16;
+    // Copies one block (128 rows x 128 bytes) whose first tap is k (k < 0: no valid row, zeros):
+    // 8 lanes copy one row; lane group `grp` owns rows 32 grp .. 32 grp + 31.
+    auto gather_block = [&](uint32_t dst, const int* cur, int k, int kb) {
+      const int k_lane = k + sub;                        // this lane's tap
+      const bool live = k >= 0 && (PACK > 1 ? k_lane < K : chunk * 8 < min(64, Cin - kb * 64));
+      const uint8_t* lane_src = data + (size_t)kb * 128 + ch_off;
+      const int* irow = cur + (live ? k_lane : 0) * TILE_R + grp * 32;
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         int4 r4 = make_int4(-1, -1, -1, -1);
-        if (irow != nullptr && live) r4 = *reinterpret_cast<const int4*>(irow + grp * 32 + 4 * q);
+        if (live) r4 = *reinterpret_cast<const int4*>(irow + 4 * q);
         const int rid[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -194,10 +212,10 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
       {
         int k = k_lo, kb = kb_lo;
         for (int m = 0; m < m_cnt; ++m) {
-          const bool v0 = (mask >> k) & 1u;
-          if (++kb == KB) { kb = 0; ++k; }
-          const bool v1 = 2 * (m_lo + m) + 1 < nblk && ((mask >> k) & 1u);
-          if (++kb == KB) { kb = 0; ++k; }
+          const bool v0 = ((mask >> k) & pmask) != 0;
+          if (++kb == KB) { kb = 0; k += PACK; }
+          const bool v1 = 2 * (m_lo + m) + 1 < nblk && ((mask >> k) & pmask) != 0;
+          if (++kb == KB) { kb = 0; k += PACK; }
           if (v0 || v1) last_m = m;
         }
       }
@@ -205,13 +223,13 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
       int k0 = k_lo, kb0 = kb_lo;
       for (int m = 0; m <= last_m && ok; ++m) {
         int k1 = k0, kb1 = kb0 + 1;               // second block of the M tile
-        if (kb1 == KB) { kb1 = 0; ++k1; }
+        if (kb1 == KB) { kb1 = 0; k1 += PACK; }
         const bool has1 = 2 * (m_lo + m) + 1 < nblk;
-        const bool v0 = (mask >> k0) & 1u;
-        const bool v1 = has1 && ((mask >> k1) & 1u);
+        const bool v0 = ((mask >> k0) & pmask) != 0;
+        const bool v1 = has1 && ((mask >> k1) & pmask) != 0;
         const int ck0 = k0, ckb0 = kb0;           // this M tile's first block
         k0 = k1; kb0 = kb1 + 1;                   // first block of the next M tile
-        if (kb0 == KB) { kb0 = 0; ++k0; }
+        if (kb0 == KB) { kb0 = 0; k0 += PACK; }
         if (!(v0 || v1) && !(mask == 0 && m == 0)) continue;
         const bool mine0 = owner == pw;
         if (++owner == PROD_WARPS) owner = 0;
@@ -226,9 +244,9 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
                        ((uint32_t)m << 8);
               mbar_arrive(full_bar(s));
             }
-            gather_block(a_dst, v0 ? cur + ck0 * TILE_R : nullptr, ckb0);
+            gather_block(a_dst, cur, v0 ? ck0 : -1, ckb0);
           } else {
-            gather_block(a_dst + BLK_BYTES, v1 ? cur + k1 * TILE_R : nullptr, has1 ? kb1 : 0);
+            gather_block(a_dst + BLK_BYTES, cur, v1 ? k1 : -1, has1 ? kb1 : 0);
           }
           cp_async_arrive_noinc(full_bar(s));
         }
@@ -356,9 +374,10 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
     const int mrow = q * 32 + lane;                    // row of the M tile = (block half, channel)
     for (int m = warp >> 2; m < m_cnt; m += 3) {
       const int b = 2 * (m_lo + m) + (mrow >> 6);
-      const int k = b / p.KB, kb = b % p.KB;
-      const int ci = kb * 64 + (mrow & 63);
-      const bool row_ok = b < p.nblk && ci < p.Cin;
+      const int e = mrow & 63;                           // element of the block: (tap, channel) when packed
+      const int k = p.PACK > 1 ? b * p.PACK + e / p.Cin : b / p.KB;
+      const int ci = p.PACK > 1 ? e % p.Cin : (b % p.KB) * 64 + e;
+      const bool row_ok = b < p.nblk && k < p.K && ci < p.Cin;
       const bool has = (touched >> m) & 1u;
       float* dst = p.partial + (((int64_t)slice * p.K + (row_ok ? k : 0)) * p.Cin + (row_ok ? ci : 0)) * p.Cout + n0;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + m * (uint32_t)p.NTW;
@@ -390,7 +409,7 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
 }
 
 struct Plan {
-  int KB, nblk, n_mt, NTW, GB, n_tiles_n, mt_per_cta, groups, stages, tmem_cols, slices;
+  int KB, PACK, nblk, n_mt, NTW, GB, n_tiles_n, mt_per_cta, groups, stages, tmem_cols, slices;
   int64_t tiles_per_slice;
   uint32_t smem_bytes;
   bool ok;
@@ -403,7 +422,8 @@ static Plan make_plan(int K, int Cin, int Cout, int64_t n_out, int dtype) {
   if (Cin < 16 || Cin % 16 != 0 || Cout < 16 || Cout % 16 != 0) return P;
   if (K < 1 || K > OC_MAX_TAPS) return P;
   P.KB = (Cin + 63) / 64;
-  P.nblk = K * P.KB;
+  P.PACK = (Cin == 16 || Cin == 32) ? 64 / Cin : 1;        // taps that share one 64-wide block
+  P.nblk = P.PACK > 1 ? (K + P.PACK - 1) / P.PACK : K * P.KB;
   P.n_mt = (P.nblk + 1) / 2;
   P.n_tiles_n = (Cout + 127) / 128;
   P.NTW = Cout <= 128 ? Cout : 128;
@@ -483,7 +503,7 @@ int launch_wgrad_tc(const WgradArgs& a, float* grad_w, void* workspace, size_t w
   prm.data = a.data; prm.gout = a.grad_out; prm.tiled = tiled;
   prm.tiled_block_bytes = (uint32_t)tile_table_block_bytes(a.K); prm.partial = (float*)workspace;
   prm.n_out = a.n_out; prm.tiles_per_slice = P.tiles_per_slice;
-  prm.K = a.K; prm.Cin = a.Cin; prm.Cout = a.Cout; prm.KB = P.KB; prm.nblk = P.nblk; prm.NTW = P.NTW;
+  prm.K = a.K; prm.Cin = a.Cin; prm.Cout = a.Cout; prm.KB = P.KB; prm.PACK = P.PACK; prm.nblk = P.nblk; prm.NTW = P.NTW;
   prm.GB = P.GB; prm.mt_per_cta = P.mt_per_cta; prm.stages = P.stages; prm.tmem_cols = P.tmem_cols;
   int rc = a.dtype == OC_BF16 ? launch_wgrad_tc_t<true>(prm, P, s) : launch_wgrad_tc_t<false>(prm, P, s);
   if (rc) return rc;
