@@ -245,6 +245,37 @@ def test_conv_large_random_table(dtype, cin, cout, n_out):
   assert_close(to_np(gb), to_np(gy.float().sum(0)), 2e-3, 'gb')
 
 
+@pytest.mark.parametrize('cin,cout', [(16, 32), (32, 16), (32, 64), (16, 16)])
+def test_conv_packed_taps_all_kernel_shapes(mid_octree, cin, cout):
+  # Cin = 16 / 32 share a 64-wide reduction block between 4 / 2 taps; with K = 8, 9, 27 taps the
+  # last block is partly padding.  Forward, transposed weights and weight gradient against fp32 torch
+  # computed from the same table, with and without the tile table.
+  octree, o = mid_octree
+  d = 6
+  for kernel, stride, nempty in [('333', 1, False), ('222', 2, False), ('313', 1, True), ('133', 2, True),
+                                 ('311', 1, False)]:
+    table, taps = octree.conv_table(d, kernel, stride, nempty)
+    tiles = octree.conv_tiles(d, kernel, stride, nempty)
+    K, n_out = len(taps), table.shape[0]
+    n_in = int(o['nnum_nempty'][d] if nempty else o['nnum'][d])
+    g = torch.Generator(device=dev()).manual_seed(K * 100 + cin)
+    x = torch.randn(n_in, cin, device=dev(), generator=g).half()
+    w = (torch.randn(K, cin, cout, device=dev(), generator=g) / (K * cin) ** 0.5).half()
+    gy = torch.randn(n_out, cout, device=dev(), generator=g).half()
+    t = table[:, taps]
+    xg = x.float()[t.clamp(min=0)] * (t >= 0).unsqueeze(-1)             # (n_out, K, cin)
+    ref_y = torch.einsum('rkc,kcd->rd', xg, w.float())
+    ref_gw = torch.einsum('rkc,rd->kcd', xg, gy.float())
+    for tl in (None, tiles):
+      y = b200.nn.conv_gather(x, w, False, None, table, taps, cin, cout, tiles=tl)
+      yt = b200.nn.conv_gather(x, w.transpose(1, 2).contiguous(), True, None, table, taps, cin, cout, tiles=tl)
+      gw, _ = b200.nn.conv_wgrad(x, gy, table, taps, cin, cout, False, tiles=tl)
+      b200._lib.status_check(dev())
+      assert_close(to_np(y), to_np(ref_y), TOL16, 'y %s' % kernel)
+      assert torch.equal(y, yt)
+      assert_close(to_np(gw), to_np(ref_gw), 2e-3, 'gw %s' % kernel)
+
+
 def test_conv_is_deterministic_and_linear(mid_octree):
   octree, o = mid_octree
   d, C = 6, 64
