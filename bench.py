@@ -506,7 +506,22 @@ def run_suite(args, b200, octree, dev):
   idx = octree.nempty_index(D)
   xne = torch.randn(idx.numel(), C, device=dev, generator=g).half()
   emit('octree_pad C=256 fp16', _time(lambda: b200.nn.octree_pad(xne, octree, D)), nbytes=(idx.numel() + n8) * C * s)
-  del x, xc, xne
+  # key search and point interpolation: 4 M query points spread over the batch, C = 96 features at depth 8
+  Ci, M = 96, 4 << 20
+  xi = torch.randn(n8, Ci, device=dev, generator=g).half()
+  q = torch.rand(M, 4, device=dev, generator=g)
+  q[:, :3] *= float(1 << D)
+  q[:, 3] = torch.floor(q[:, 3] * BATCH).clamp(max=BATCH - 1)
+  # half of the queries sit on occupied cells, so that the gathers are real work
+  cx, cy, cz, cb = octree.xyzb(D)
+  pick = torch.randint(0, n8, (M // 2,), device=dev, generator=g)
+  q[:M // 2] = torch.stack([cx[pick], cy[pick], cz[pick], cb[pick]], 1).float() + torch.tensor([0.3, 0.6, 0.4, 0.0], device=dev)
+  emit('search_xyzb depth8 (4.2 M queries)', _time(lambda: octree.search_xyzb(q, D)), nbytes=M * (16 + 8 + 8) , rows=M)
+  emit('octree_nearest_pts C=96 fp16', _time(lambda: b200.nn.octree_nearest_pts(xi, octree, D, q)),
+       nbytes=M * (16 + 8) + M * Ci * s * 3 // 2, rows=M)
+  emit('octree_linear_pts C=96 fp16', _time(lambda: b200.nn.octree_linear_pts(xi, octree, D, q)),
+       nbytes=M * (16 + 8 * 12) + M * Ci * s, rows=M)
+  del x, xc, xne, xi, q
   # octree construction: config 4 shape (200k points per cloud, depth 10), bounded to 16 clouds
   import ocnn_pytorch_b200 as B
   nb, npts, depth = 16, 200000, 10

@@ -143,6 +143,40 @@ int oc_neigh_variant(const int64_t* neigh, const int32_t* children, const int64_
 int oc_neigh_inverse(const void* table, int idx_bytes, int64_t n_rows, int table_cols,
                      const int* h_taps, int K, int64_t n_targets, int32_t* inv, void* stream);
 
+/* ---- Key search and point interpolation ------------------------------------ */
+
+/* Octree.search_key, ocnn/octree/octree.py:464-488: idx[i] = position of query[i] in the
+ * ascending node keys keys[0..n) (all nodes of a depth, or its non-empty nodes), -1 if absent.
+ * Octree.search_xyzb (:448-462) = oc_xyz2key on the query coordinates, then this. */
+int oc_search_key(const int64_t* keys, int64_t n, const int64_t* query, int64_t m, int64_t* idx,
+                  void* stream);
+
+/* Steps 1-2 of octree_linear_pts, ocnn/nn/octree_interp.py:63-88, for points pts (m,4) =
+ * (x, y, z, batch) already scaled to [0, 2^depth): the 8 cell centres around each point,
+ * idx8 (m,8) = their rows among `keys` or -1 (also outside [0, 2^depth) when bound_check;
+ * without it coordinates wrap modulo 2^depth exactly as xyz2key does), w8 (m,8) fp32 =
+ * |prod_d ((1 - g_d) - frac_d)|. */
+int oc_interp_corners(const int64_t* keys, int64_t n, const float* pts, int64_t m, int depth,
+                      int bound_check, int64_t* idx8, float* w8, void* stream);
+
+/* octree_nearest_pts, ocnn/nn/octree_interp.py:16-48: out[p] = data[idx[p]] or 0 where
+ * idx[p] < 0; and its gradient acc[idx[p]] += grad[p] (fp32 accumulator of the caller,
+ * zeroed by the caller, atomics because points share rows: order of summation not fixed,
+ * as in the reference's index_add). */
+int oc_rows_gather(const void* data, const int64_t* idx, int64_t m, int C, int dtype, void* out,
+                   void* stream);
+int oc_rows_scatter_add(const void* grad, const int64_t* idx, int64_t m, int C, int dtype, float* acc,
+                        void* stream);
+
+/* Step 3 of octree_linear_pts (:90-98, the reference multiplies a sparse COO matrix):
+ *   out[p] = sum_j w8[p,j] data[idx8[p,j]] / (sum_j w8[p,j] + 1e-12)  over the corners with idx >= 0,
+ * and the gradient with respect to data, acc[idx8[p,j]] += w8[p,j] / (sum + 1e-12) * grad_out[p]
+ * (fp32 accumulator as above). */
+int oc_interp_linear_fwd(const void* data, const int64_t* idx8, const float* w8, int64_t m, int C,
+                         int dtype, void* out, void* stream);
+int oc_interp_linear_bwd(const void* grad_out, const int64_t* idx8, const float* w8, int64_t m, int C,
+                         int dtype, float* acc, void* stream);
+
 /* ---- Octree convolution -------------------------------------------------- */
 
 /* Gather-GEMM, the forward of ocnn/nn/octree_conv.py:115-143 (forward_gemm) and

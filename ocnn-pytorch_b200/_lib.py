@@ -41,6 +41,12 @@ PROTOTYPES = {
     'oc_nempty_index': (_i, [_vp, _i64, _vp, _vp, _sz, _vp]),
     'oc_neigh_variant': (_i, [_vp, _vp, _vp, _i64, _i64, _ip, _i, _vp, _i, _vp]),
     'oc_neigh_inverse': (_i, [_vp, _i, _i64, _i, _ip, _i, _i64, _vp, _vp]),
+    'oc_search_key': (_i, [_vp, _i64, _vp, _i64, _vp, _vp]),
+    'oc_interp_corners': (_i, [_vp, _i64, _vp, _i64, _i, _i, _vp, _vp, _vp]),
+    'oc_rows_gather': (_i, [_vp, _vp, _i64, _i, _i, _vp, _vp]),
+    'oc_rows_scatter_add': (_i, [_vp, _vp, _i64, _i, _i, _vp, _vp]),
+    'oc_interp_linear_fwd': (_i, [_vp, _vp, _vp, _i64, _i, _i, _vp, _vp]),
+    'oc_interp_linear_bwd': (_i, [_vp, _vp, _vp, _i64, _i, _i, _vp, _vp]),
     'oc_conv_workspace_bytes': (_sz, [_i, _i, _i, _i]),
     'oc_conv_fwd': (_i, [_vp, _i64, _vp, _i, _i, _vp, _vp, _i, _i, _ip, _i, _i64, _i, _i, _i, _vp,
                          _vp, _sz, _vp]),

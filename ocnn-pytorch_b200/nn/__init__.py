@@ -4,7 +4,8 @@ from .octree_conv import (OctreeConv, OctreeDeconv, octree_conv, octree_deconv,
                           tile_table, tiled_supported)
 from .octree_dwconv import OctreeDWConv, octree_dwconv
 from .octree_pool import (octree_max_pool, octree_max_unpool, OctreeMaxPool, OctreeMaxUnpool)
-from .octree_interp import octree_nearest_upsample, OctreeUpsample
+from .octree_interp import (octree_nearest_upsample, OctreeUpsample, octree_nearest_pts,
+                            octree_linear_pts, OctreeInterp)
 from .octree_norm import (OctreeBatchNorm, OctreeGroupNorm, OctreeInstanceNorm, OctreeNorm,
                           convert_sync_batchnorm, col_stats)
 
@@ -12,6 +13,6 @@ __all__ = [
     'octree_pad', 'octree_depad', 'OctreeConv', 'OctreeDeconv', 'octree_conv', 'octree_deconv',
     'OctreeConvFunction', 'OctreeDeconvFunction', 'conv_gather', 'conv_wgrad', 'tile_table', 'tiled_supported', 'OctreeDWConv',
     'octree_dwconv', 'octree_max_pool', 'octree_max_unpool', 'OctreeMaxPool', 'OctreeMaxUnpool',
-    'octree_nearest_upsample', 'OctreeUpsample', 'OctreeBatchNorm', 'OctreeGroupNorm',
+    'octree_nearest_upsample', 'OctreeUpsample', 'octree_nearest_pts', 'octree_linear_pts', 'OctreeInterp', 'OctreeBatchNorm', 'OctreeGroupNorm',
     'OctreeInstanceNorm', 'OctreeNorm', 'convert_sync_batchnorm', 'col_stats',
 ]

@@ -420,11 +420,12 @@ class Octree:
   def search_key(self, query: torch.Tensor, depth: int, nempty: bool = False):
     r''' Index of each query key among the node keys, -1 if absent
     (octree.py:464-488). '''
-    key = self.key(depth, nempty)
-    idx = torch.searchsorted(key, query)
-    valid = idx < key.shape[0]
-    found = key[idx.clamp(max=key.shape[0] - 1)] == query
-    idx[~(valid & found)] = -1
+    key = self.key(depth, nempty).contiguous()
+    query = query.long().contiguous()
+    _lib.require_cuda(key, query)
+    idx = torch.empty_like(query)
+    _lib.call('oc_search_key', _lib.ptr(key), key.numel(), _lib.ptr(query), query.numel(),
+              _lib.ptr(idx), self._stream())
     return idx
 
   # ------------------------------------------------------------- features

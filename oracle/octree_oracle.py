@@ -352,3 +352,84 @@ def group_norm(x, batch_id, batch_size, group, weights, bias, eps=1e-5):
   inv_std = 1.0 / np.sqrt(var + eps)
   out = out * inv_std[batch_id]
   return out * weights.reshape(1, -1) + bias.reshape(1, -1)
+
+
+# ---------------------------------------------------------------- key search, point interpolation
+def search_key(keys, query):
+  '''Octree.search_key, ocnn/octree/octree.py:464-488: position of each query key in the
+  sorted node keys, -1 if absent.'''
+  keys = np.asarray(keys, dtype=np.int64)
+  query = np.asarray(query, dtype=np.int64)
+  idx = np.searchsorted(keys, query)
+  ok = idx < keys.shape[0]
+  ok[ok] = keys[idx[ok]] == query[ok]
+  return np.where(ok, idx, -1).astype(np.int64)
+
+
+def search_xyzb(keys, query, depth):
+  '''Octree.search_xyzb, ocnn/octree/octree.py:448-462 (coordinates are truncated by xyz2key).'''
+  return search_key(keys, xyz2key(query[:, 0], query[:, 1], query[:, 2], query[:, 3], depth))
+
+
+def nearest_pts(data, keys, depth, pts, bound_check=False):
+  '''octree_nearest_pts, ocnn/nn/octree_interp.py:16-48.  `keys`: the node keys that the rows of
+  `data` belong to (all nodes, or the non-empty ones).  Returns (out, idx with -1 = no row).'''
+  idx = search_xyzb(keys, pts, depth)
+  valid = idx > -1
+  if bound_check:
+    valid &= np.logical_and(pts[:, :3] >= 0, pts[:, :3] < 2 ** depth).all(1)
+  out = np.zeros((pts.shape[0], data.shape[1]), dtype=data.dtype)
+  out[valid] = data[idx[valid]]
+  return out, np.where(valid, idx, -1)
+
+
+def nearest_pts_backward(grad, idx, n_rows):
+  '''Gradient of nearest_pts with respect to data: rows of grad added at idx (>= 0).'''
+  gd = np.zeros((n_rows, grad.shape[1]), dtype=np.float64)
+  v = idx >= 0
+  np.add.at(gd, idx[v], grad[v].astype(np.float64))
+  return gd.astype(grad.dtype)
+
+
+_GRID = np.array([[0, 0, 0], [0, 0, 1], [0, 1, 0], [0, 1, 1],
+                  [1, 0, 0], [1, 0, 1], [1, 1, 0], [1, 1, 1]], dtype=np.float32)
+
+
+def linear_corners(keys, depth, pts, bound_check=False):
+  '''Steps 1-2 of octree_linear_pts, ocnn/nn/octree_interp.py:63-88: the 8 surrounding cell
+  centres of every point as (idx (N,8) with -1 = absent, weight (N,8) float32).'''
+  xyzf = pts[:, :3].astype(np.float32) - np.float32(0.5)
+  xyzi = np.floor(xyzf)
+  frac = xyzf - xyzi
+  xyzn = (xyzi[:, None, :] + _GRID[None]).reshape(-1, 3)
+  batch = np.repeat(pts[:, 3], 8)
+  idx = search_xyzb(keys, np.concatenate([xyzn, batch[:, None]], axis=1), depth)
+  valid = idx > -1
+  if bound_check:
+    valid &= np.logical_and(xyzn >= 0, xyzn < 2 ** depth).all(1)
+  w = np.abs(np.prod((np.float32(1.0) - _GRID)[None] - frac[:, None, :], axis=2)).astype(np.float32)
+  return np.where(valid, idx, -1).reshape(-1, 8), w
+
+
+def linear_pts(data, keys, depth, pts, bound_check=False):
+  '''octree_linear_pts, ocnn/nn/octree_interp.py:51-98: weighted mean of the existing corners,
+  out = (sum_j w_j data[idx_j]) / (sum_j w_j + 1e-12).'''
+  idx, w = linear_corners(keys, depth, pts, bound_check)
+  v = idx >= 0
+  wv = np.where(v, w, 0).astype(np.float64)
+  g = data.astype(np.float64)[np.where(v, idx, 0)]                 # (N, 8, C)
+  out = (g * wv[:, :, None]).sum(1)
+  norm = wv.sum(1, keepdims=True)
+  return (out / (norm + 1e-12)).astype(data.dtype)
+
+
+def linear_pts_backward(grad, keys, depth, pts, n_rows, bound_check=False):
+  '''Gradient of linear_pts with respect to data.'''
+  idx, w = linear_corners(keys, depth, pts, bound_check)
+  v = idx >= 0
+  wv = np.where(v, w, 0).astype(np.float64)
+  coef = wv / (wv.sum(1, keepdims=True) + 1e-12)                   # (N, 8)
+  gd = np.zeros((n_rows, grad.shape[1]), dtype=np.float64)
+  contrib = coef[:, :, None] * grad.astype(np.float64)[:, None, :]
+  np.add.at(gd, idx[v], contrib[v])
+  return gd.astype(grad.dtype)

@@ -11,6 +11,9 @@ kernels or oracle):
   octrees.npz    the reference's fixtures test/data/octree/test_00{1..5}.npz
                  (points, normals and their stored key/child/nnum) re-packed
   batch45.npz    test/data/batch_45.npz re-packed (merged octree 4+5 incl. neigh)
+  interp.npz     test/data/search_key.npz and test/data/interp.npz re-packed (queries and
+                 the stored answers for the merged octree 4+5), plus the reference's
+                 gradients, bound_check and out-of-range behaviour on seeded points
   synthetic.npz  a small seeded batch: octree, neighbour tables and variants,
                  conv / deconv / dwconv forward + gradients, pooling, upsampling,
                  normalisation, key encode/decode edge cases
@@ -83,6 +86,68 @@ def ref_fixtures():
   np.savez_compressed(os.path.join(OUT, 'batch45.npz'), depth=d['depth'], full_depth=d['full_depth'],
                       key=d['key'], child=d['child'], nnum=d['nnum'], nnum_nempty=d['nnum_nempty'],
                       feature=d['feature'][:, :3], neigh=d['neigh'])
+
+
+def interp():
+  """Key search and point interpolation (test_octree.py:138-155, test_octree_interp.py:20-42)."""
+  out = {}
+  octs = []
+  for i in (4, 5):
+    d = np.load(os.path.join(REF, 'test/data/octree/test_%03d.npz' % i))
+    pc = ocnn.octree.Points(torch.from_numpy(d['points']), torch.from_numpy(d['normals']))
+    o = ocnn.octree.Octree(d['depth'].item(), d['full_depth'].item())
+    o.build_octree(pc)
+    octs.append(o)
+  octree = ocnn.octree.merge_octrees(octs)
+  octree.construct_all_neigh()
+  depth = 5
+  sk = np.load(os.path.join(REF, 'test/data/search_key.npz'))
+  xyzb = torch.from_numpy(sk['xyzb']).long()
+  key = ocnn.octree.xyz2key(xyzb[:, 0], xyzb[:, 1], xyzb[:, 2], xyzb[:, 3], depth)
+  # the stored answers are what the reference's own test compares against
+  assert np.array_equal(octree.search_key(key, depth, False).numpy(), sk['idx'])
+  assert np.array_equal(octree.search_key(key, depth, True).numpy(), sk['idx_ne'])
+  out['sk_xyzb'], out['sk_idx'], out['sk_idx_ne'] = sk['xyzb'], sk['idx'], sk['idx_ne']
+
+  it = np.load(os.path.join(REF, 'test/data/interp.npz'))
+  data = torch.from_numpy(it['data'])
+  pts = torch.from_numpy(it['pts'])
+  data_ne = ocnn.nn.octree_depad(data, octree, depth)
+  for name, fn in (('linear', ocnn.nn.octree_linear_pts), ('near', ocnn.nn.octree_nearest_pts)):
+    for ne, dd in ((False, data), (True, data_ne)):
+      got = fn(dd, octree, depth, pts, nempty=ne)
+      assert np.allclose(got.numpy(), it[name + ('_ne' if ne else '')], atol=1e-6)
+  for k in ('pts', 'data', 'linear', 'linear_ne', 'near', 'near_ne'):
+    out['it_' + k] = it[k]
+
+  # gradients, bound_check, points outside the box and the module with rescaling (seeded)
+  g = torch.Generator().manual_seed(5)
+  C = 6
+  pts2 = torch.rand(3000, 4, generator=g)
+  pts2[:, :3] = pts2[:, :3] * 36.0 - 2.0              # a band of 2 cells outside [0, 32) on every side
+  pts2[:, 3] = (pts2[:, 3] > 0.5).float()
+  out['g_pts'] = pts2.numpy()
+  for ne in (False, True):
+    n = int(octree.nnum_nempty[depth] if ne else octree.nnum[depth])
+    dd = torch.randn(n, C, generator=g, requires_grad=True)
+    gy = torch.randn(3000, C, generator=g)
+    tag = '_ne' if ne else ''
+    out['g_data' + tag] = dd.detach().numpy()
+    out['g_gy' + tag] = gy.numpy()
+    for name, fn in (('linear', ocnn.nn.octree_linear_pts), ('near', ocnn.nn.octree_nearest_pts)):
+      for bc in (False, True):
+        dd.grad = None
+        y = fn(dd, octree, depth, pts2.clone(), nempty=ne, bound_check=bc)
+        y.backward(gy)
+        out['g_%s%s_bc%d' % (name, tag, int(bc))] = y.detach().numpy()
+        out['g_%s%s_bc%d_grad' % (name, tag, int(bc))] = dd.grad.numpy().copy()
+  m = ocnn.nn.OctreeInterp('linear', nempty=True, bound_check=True, rescale_pts=True)
+  praw = torch.rand(500, 4, generator=g) * 2 - 1
+  praw[:, 3] = (praw[:, 3] > 0).float()
+  out['m_pts'] = praw.numpy().copy()
+  dd = torch.from_numpy(out['g_data_ne'])
+  out['m_out'] = m(dd, octree, depth, praw.clone()).numpy()
+  np.savez_compressed(os.path.join(OUT, 'interp.npz'), **out)
 
 
 def synthetic():
@@ -252,6 +317,7 @@ def synthetic():
 if __name__ == '__main__':
   hand3()
   ref_fixtures()
+  interp()
   synthetic()
   for f in sorted(os.listdir(OUT)):
     if f.endswith('.npz'):

@@ -188,3 +188,35 @@ def test_norms(golden):
   n = syn['bn_x'].shape[0]
   assert np.allclose(0.1 * mean, syn['bn_rm'], atol=1e-6)
   assert np.allclose(0.9 + 0.1 * var * n / (n - 1), syn['bn_rv'], atol=1e-6)
+
+
+def test_search_and_interp_against_reference(golden):
+  # key search and point interpolation of the merged octree 4+5: the reference's stored answers
+  # (test/data/search_key.npz, test/data/interp.npz) and its gradients on seeded points
+  d, b45, it = golden['octrees'], golden['batch45'], golden['interp']
+  depth = 5
+  nnum = b45['nnum']
+  off = int(nnum[:depth].sum())
+  keys = b45['key'][off:off + int(nnum[depth])]
+  child = b45['child'][off:off + int(nnum[depth])]
+  keys_ne = keys[child >= 0]
+  xyzb = it['sk_xyzb'].astype(np.int64)
+  q = orc.xyz2key(xyzb[:, 0], xyzb[:, 1], xyzb[:, 2], xyzb[:, 3], depth)
+  assert np.array_equal(orc.search_key(keys, q), it['sk_idx'])
+  assert np.array_equal(orc.search_key(keys_ne, q), it['sk_idx_ne'])
+  data, pts = it['it_data'], it['it_pts']
+  data_ne = data[child >= 0]
+  assert np.allclose(orc.linear_pts(data, keys, depth, pts), it['it_linear'], atol=1e-6)
+  assert np.allclose(orc.linear_pts(data_ne, keys_ne, depth, pts), it['it_linear_ne'], atol=1e-6)
+  assert np.allclose(orc.nearest_pts(data, keys, depth, pts)[0], it['it_near'], atol=1e-6)
+  assert np.allclose(orc.nearest_pts(data_ne, keys_ne, depth, pts)[0], it['it_near_ne'], atol=1e-6)
+  gp = it['g_pts']
+  for tag, kk in (('', keys), ('_ne', keys_ne)):
+    dd, gy = it['g_data' + tag], it['g_gy' + tag]
+    for bc in (0, 1):
+      y, idx = orc.nearest_pts(dd, kk, depth, gp, bool(bc))
+      assert np.allclose(y, it['g_near%s_bc%d' % (tag, bc)], atol=1e-6)
+      assert np.allclose(orc.nearest_pts_backward(gy, idx, dd.shape[0]), it['g_near%s_bc%d_grad' % (tag, bc)], atol=1e-5)
+      assert np.allclose(orc.linear_pts(dd, kk, depth, gp, bool(bc)), it['g_linear%s_bc%d' % (tag, bc)], atol=1e-5)
+      assert np.allclose(orc.linear_pts_backward(gy, kk, depth, gp, dd.shape[0], bool(bc)),
+                         it['g_linear%s_bc%d_grad' % (tag, bc)], atol=1e-5)
