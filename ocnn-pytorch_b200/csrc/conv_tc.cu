@@ -7,23 +7,26 @@
 // conv_bwd_input_implicit_gemm(_splitk) (ocnn/nn/kernels/*.py) and the im2col +
 // torch.mm path of ocnn/nn/octree_conv.py:115-168.
 //
-// One persistent CTA per SM walks 128-row output tiles.  Warp roles:
+// One persistent CTA per SM walks output tiles of H x 128 rows (H = 1, or 2 when a tile
+// table is given and Cout <= 128).  Warp roles:
 //   warps 0-3  epilogue : TMEM -> registers -> (+bias, cast) -> global
-//   warps 5-7, 9-11, 13-14 producers: prefetch the tile's neighbour indices and publish them in
-//                         shared memory, then issue the stages; stage = (tap,
-//                         64-channel block).  A operand: the 128 gathered input rows,
-//                         copied by cp.async (16 B per lane, 8 lanes per row,
-//                         zero-fill for missing neighbours) into the 128-byte-
-//                         swizzled K-major layout the MMA reads; each thread's
-//                         completion arrives on the stage barrier, nobody waits.
-//                         B operand: the matching block of the pre-swizzled weight
-//                         image, one bulk copy.  Taps with no valid neighbour in
-//                         the whole tile are skipped (warp-OR of the index signs).
-//   warp 4     MMA issuer: tcgen05.mma 128 x Cout x 16 per K step, accumulators
-//                         double-buffered in TMEM so the epilogue of tile i
-//                         overlaps the main loop of tile i+1.
-// Stages flow through a ring of full/empty mbarriers; a per-stage header tells
-// the MMA warp whether the stage starts or ends a tile.  Every wait is bounded.
+//   warp 4     MMA issuer: all 32 lanes run the loop, an elected lane issues tcgen05.mma
+//                         128 x Cout x 16 per K step; accumulators double-buffered in TMEM
+//                         so the epilogue of tile i overlaps the main loop of tile i+1.
+//   warp 8     loader   : one bulk copy per 128-row half brings that half's block of the tile
+//                         table (tap mask + tap-major int32 indices) into shared memory.
+//   warps 5-7, 9-11, 13-14 producers: a stage = one reduction block (a tap x 64 channels, or
+//                         2 / 4 whole taps when Cin = 32 / 16): per half the 128 gathered
+//                         input rows, copied by cp.async (16 B per lane, 8 lanes per row,
+//                         zero-fill for missing neighbours) into the 128-byte-swizzled
+//                         K-major layout the MMA reads, plus the matching block of the
+//                         pre-swizzled weight image (one bulk copy).  Whole blocks are dealt
+//                         to the warps round-robin; each lane's completion arrives on the
+//                         stage barrier, nobody waits.  Blocks whose taps have no valid
+//                         neighbour in the whole tile are skipped.  Given a plain table
+//                         (H = 1) the producers prefetch and publish the indices themselves.
+// Stages flow through a ring of full/empty mbarriers; the header of a tile's first stage
+// tells the MMA warp how many stages the tile has.  Every wait is bounded.
 #include "oc_common.cuh"
 #include "conv_internal.cuh"
 #include "tc_ptx.cuh"
@@ -54,7 +57,7 @@ namespace tc {
 constexpr int TILE_M = 128;
 constexpr int KBLK = 64;                 // channels per K block = one 128-byte swizzle row
 constexpr int A_BYTES = TILE_M * 128;    // 16 KB
-constexpr int PROD_WARPS = 8;             // warps 4..11 gather; warp 12 issues the MMAs
+constexpr int PROD_WARPS = 8;             // gathering warps
 constexpr int PROD_THREADS = PROD_WARPS * 32;
 constexpr int FSPLIT = PROD_THREADS / TILE_M;    // threads that share the index prefetch of one row
 // Warp roles by index: 0-3 epilogue, 4 MMA issuer, producers = the warps > 4 whose index is
