@@ -48,6 +48,26 @@ struct RowIO<T, false> {
   __device__ static __forceinline__ void store(T* p, const float* v) { *p = from_f32<T>(v[0]); }
 };
 
+// Grid-stride walk over (row, 16-byte chunk of the row) pairs without a division per step:
+// the pair advances by (stride / cpr, stride % cpr) with one carry.
+struct RowChunkIter {
+  int64_t row, drow;
+  int col, dcol, cpr;
+  __device__ __forceinline__ explicit RowChunkIter(int cpr_) : cpr(cpr_) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t t0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    drow = stride / cpr;
+    dcol = (int)(stride % cpr);
+    row = t0 / cpr;
+    col = (int)(t0 % cpr);
+  }
+  __device__ __forceinline__ void next() {
+    row += drow;
+    col += dcol;
+    if (col >= cpr) { col -= cpr; ++row; }
+  }
+};
+
 // ---------------------------------------------------------------------------
 // depth-wise convolution
 // ---------------------------------------------------------------------------
@@ -57,10 +77,9 @@ __global__ void dwconv_kernel(const T* __restrict__ data, const float* __restric
                               int64_t n_out, int C, T* __restrict__ out) {
   constexpr int N = RowIO<T, VEC>::N;
   const int cpr = C / N;  // chunks per row
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n_out * cpr;
-       t += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = t / cpr;
-    const int c0 = (int)(t - r * cpr) * N;
+  for (RowChunkIter it(cpr); it.row < n_out; it.next()) {
+    const int64_t r = it.row;
+    const int c0 = it.col * N;
     float acc[N];
 #pragma unroll
     for (int i = 0; i < N; ++i) acc[i] = 0.f;
@@ -197,10 +216,9 @@ __global__ void index_rows_kernel(const T* __restrict__ data, const int64_t* __r
                                   int64_t n, int C, T* __restrict__ out) {
   constexpr int N = RowIO<T, VEC>::N;
   const int cpr = C / N;
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n * cpr;
-       t += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t j = t / cpr;
-    const int c0 = (int)(t - j * cpr) * N;
+  for (RowChunkIter it(cpr); it.row < n; it.next()) {
+    const int64_t j = it.row;
+    const int c0 = it.col * N;
     const int64_t q = index[j];
     float v[N];
     RowIO<T, VEC>::load(data + (SCATTER ? j : q) * C + c0, v);
@@ -217,10 +235,9 @@ __global__ void maxpool_fwd_kernel(const T* __restrict__ data, const int32_t* __
                                    T* __restrict__ out, int64_t* __restrict__ argmax) {
   constexpr int N = RowIO<T, VEC>::N;
   const int cpr = C / N;
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n_out * cpr;
-       t += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t p = t / cpr;
-    const int c0 = (int)(t - p * cpr) * N;
+  for (RowChunkIter it(cpr); it.row < n_out; it.next()) {
+    const int64_t p = it.row;
+    const int c0 = it.col * N;
     const int64_t j = child_out ? (int64_t)child_out[p] : p;
     float best[N];
     int arg[N];
@@ -257,10 +274,9 @@ __global__ void maxpool_bwd_kernel(const T* __restrict__ gout, const int64_t* __
                                    T* __restrict__ gin) {
   constexpr int N = RowIO<T, VEC>::N;
   const int cpr = C / N;
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n_out * cpr;
-       t += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t p = t / cpr;
-    const int c0 = (int)(t - p * cpr) * N;
+  for (RowChunkIter it(cpr); it.row < n_out; it.next()) {
+    const int64_t p = it.row;
+    const int c0 = it.col * N;
     const int64_t j = child_out ? (int64_t)child_out[p] : p;
     if (j < 0) continue;
     float g[N];
@@ -285,10 +301,9 @@ __global__ void upsample_fwd_kernel(const T* __restrict__ data, const int64_t* _
                                     T* __restrict__ out) {
   constexpr int N = RowIO<T, VEC>::N;
   const int cpr = C / N;
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n_out * cpr;
-       t += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t m = t / cpr;
-    const int c0 = (int)(t - m * cpr) * N;
+  for (RowChunkIter it(cpr); it.row < n_out; it.next()) {
+    const int64_t m = it.row;
+    const int c0 = it.col * N;
     const int64_t src = idx_coarse ? idx_coarse[m >> 3] : (idx_fine[m] >> 3);
     float v[N];
     RowIO<T, VEC>::load(data + src * C + c0, v);
@@ -302,10 +317,9 @@ __global__ void upsample_bwd_kernel(const T* __restrict__ gout, const int32_t* _
                                     T* __restrict__ gin) {
   constexpr int N = RowIO<T, VEC>::N;
   const int cpr = C / N;
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n_in * cpr;
-       t += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t q = t / cpr;
-    const int c0 = (int)(t - q * cpr) * N;
+  for (RowChunkIter it(cpr); it.row < n_in; it.next()) {
+    const int64_t q = it.row;
+    const int c0 = it.col * N;
     float acc[N];
 #pragma unroll
     for (int i = 0; i < N; ++i) acc[i] = 0.f;
