@@ -143,6 +143,31 @@ int oc_neigh_variant(const int64_t* neigh, const int32_t* children, const int64_
 int oc_neigh_inverse(const void* table, int idx_bytes, int64_t n_rows, int table_cols,
                      const int* h_taps, int K, int64_t n_targets, int32_t* inv, void* stream);
 
+/* ---- Average / global pooling, per-octree scaling ------------------------------ */
+
+/* octree_avg_pool, ocnn/nn/octree_pool.py:68-103 (the reference multiplies a sparse COO matrix):
+ *   out[r] = v_r * sum_k data[table[r, taps[k]]],  v_r = 1 / (#entries >= 0 + 1e-8);  val[r] = v_r
+ * (fp32, may be NULL).  Gradient: grad_in[n] = sum_k val[t] * grad_out[t], t = table_t[n, taps_t[k]],
+ * with the mirrored / inverse table of the scatter direction (as for oc_conv_fwd). */
+int oc_avgpool_fwd(const void* data, const void* table, int idx_bytes, int table_cols,
+                   const int* h_taps, int K, int64_t n_out, int C, int dtype, void* out, float* val,
+                   void* stream);
+int oc_avgpool_bwd(const void* grad_out, const float* val, const void* table_t, int idx_bytes,
+                   int table_cols, const int* h_taps, int K, int64_t n_in, int C, int dtype,
+                   void* grad_in, void* stream);
+
+/* octree_global_pool, ocnn/nn/octree_pool.py:106-124: mean[b] = sum of the rows of octree b /
+ * max(count_b, 1), fp32 (batch, C).  h_offsets (batch+1, host): row ranges of the octrees
+ * (oc_batch_offsets); rows of one octree are contiguous. */
+size_t oc_global_pool_workspace_bytes(int64_t n, int batch, int C);
+int oc_global_pool_fwd(const void* data, const int64_t* h_offsets, int batch, int C, int dtype,
+                       float* mean, void* workspace, size_t workspace_bytes, void* stream);
+
+/* out[r] = data[r] * scale[b] for the rows of octree b: the per-octree mask of OctreeDropPath
+ * (ocnn/nn/octree_drop.py:14-60) and the gradient of the global mean; scale: device, fp32 (batch). */
+int oc_scale_segments(const void* data, const int64_t* h_offsets, int batch, const float* scale, int C,
+                      int dtype, void* out, void* stream);
+
 /* ---- Key search and point interpolation ------------------------------------ */
 
 /* Octree.search_key, ocnn/octree/octree.py:464-488: idx[i] = position of query[i] in the

@@ -41,6 +41,11 @@ PROTOTYPES = {
     'oc_nempty_index': (_i, [_vp, _i64, _vp, _vp, _sz, _vp]),
     'oc_neigh_variant': (_i, [_vp, _vp, _vp, _i64, _i64, _ip, _i, _vp, _i, _vp]),
     'oc_neigh_inverse': (_i, [_vp, _i, _i64, _i, _ip, _i, _i64, _vp, _vp]),
+    'oc_avgpool_fwd': (_i, [_vp, _vp, _i, _i, _ip, _i, _i64, _i, _i, _vp, _vp, _vp]),
+    'oc_avgpool_bwd': (_i, [_vp, _vp, _vp, _i, _i, _ip, _i, _i64, _i, _i, _vp, _vp]),
+    'oc_global_pool_workspace_bytes': (_sz, [_i64, _i, _i]),
+    'oc_global_pool_fwd': (_i, [_vp, _i64p, _i, _i, _i, _vp, _vp, _sz, _vp]),
+    'oc_scale_segments': (_i, [_vp, _i64p, _i, _vp, _i, _i, _vp, _vp]),
     'oc_search_key': (_i, [_vp, _i64, _vp, _i64, _vp, _vp]),
     'oc_interp_corners': (_i, [_vp, _i64, _vp, _i64, _i, _i, _vp, _vp, _vp]),
     'oc_rows_gather': (_i, [_vp, _vp, _i64, _i, _i, _vp, _vp]),

@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, 'csrc')
 LIB = os.path.join(HERE, 'liboctconv.so')
 SOURCES = ['api.cu', 'keys.cu', 'build.cu', 'neigh.cu', 'conv_fma.cu', 'conv_tc.cu',
-           'elementwise.cu', 'norm.cu', 'interp.cu']
+           'elementwise.cu', 'norm.cu', 'interp.cu', 'pool_extra.cu']
 NVCC_FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17',
               '--extended-lambda', '-Xcompiler', '-fPIC', '-Xcompiler', '-fvisibility=default']
 

@@ -433,3 +433,54 @@ def linear_pts_backward(grad, keys, depth, pts, n_rows, bound_check=False):
   contrib = coef[:, :, None] * grad.astype(np.float64)[:, None, :]
   np.add.at(gd, idx[v], contrib[v])
   return gd.astype(grad.dtype)
+
+
+# ---------------------------------------------------------------- average / global pooling, align, voxels
+def avg_pool(data, neigh):
+  '''octree_avg_pool, ocnn/nn/octree_pool.py:68-103: mean over the existing entries of each row of
+  the neighbour table, weight 1 / (count + 1e-8).  Returns (out, val) with val the row weights.'''
+  mask = neigh >= 0
+  val = (1.0 / (mask.sum(1) + 1e-8)).astype(np.float32)
+  g = data.astype(np.float64)[np.where(mask, neigh, 0)] * mask[:, :, None]
+  return (g.sum(1) * val[:, None].astype(np.float64)).astype(data.dtype), val
+
+
+def avg_pool_backward(grad, neigh, n_in):
+  '''Gradient of avg_pool with respect to data.'''
+  mask = neigh >= 0
+  val = 1.0 / (mask.sum(1) + 1e-8)
+  gd = np.zeros((n_in, grad.shape[1]), dtype=np.float64)
+  r, k = np.nonzero(mask)
+  np.add.at(gd, neigh[r, k], grad.astype(np.float64)[r] * val[r, None])
+  return gd.astype(grad.dtype)
+
+
+def global_pool(data, batch_id, batch_size):
+  '''octree_global_pool, ocnn/nn/octree_pool.py:106-124: per-octree mean (count clamped to >= 1).
+  Returns (out, count).'''
+  count = np.bincount(batch_id, minlength=batch_size).astype(np.float64)
+  count[count < 1] = 1
+  s = np.zeros((batch_size, data.shape[1]), dtype=np.float64)
+  np.add.at(s, batch_id, data.astype(np.float64))
+  return (s / count[:, None]).astype(data.dtype), count
+
+
+def global_pool_backward(grad, batch_id, count):
+  return (grad.astype(np.float64)[batch_id] / count[batch_id, None]).astype(grad.dtype)
+
+
+def align(value, key, query):
+  '''search_value / octree_align, ocnn/nn/octree_align.py:13-48: value of the node with the same
+  key, zeros where the query key does not exist.  Returns (out fp32, idx).'''
+  idx = search_key(key, query)
+  out = np.zeros((query.shape[0], value.shape[1]), dtype=np.float32)
+  out[idx >= 0] = value[idx[idx >= 0]]
+  return out, idx
+
+
+def octree2voxel(data, x, y, z, b, depth, batch_size):
+  '''octree2voxel, ocnn/nn/octree2vox.py:13-31.'''
+  num = 1 << depth
+  vox = np.zeros((batch_size, num, num, num, data.shape[1]), dtype=data.dtype)
+  vox[b, x, y, z] = data
+  return vox

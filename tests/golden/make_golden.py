@@ -14,6 +14,8 @@ kernels or oracle):
   interp.npz     test/data/search_key.npz and test/data/interp.npz re-packed (queries and
                  the stored answers for the merged octree 4+5), plus the reference's
                  gradients, bound_check and out-of-range behaviour on seeded points
+  extras.npz     average / global pooling, octree_align, octree2voxel on the merged octree 4+5
+                 (forward and gradients, seeded features)
   synthetic.npz  a small seeded batch: octree, neighbour tables and variants,
                  conv / deconv / dwconv forward + gradients, pooling, upsampling,
                  normalisation, key encode/decode edge cases
@@ -148,6 +150,62 @@ def interp():
   dd = torch.from_numpy(out['g_data_ne'])
   out['m_out'] = m(dd, octree, depth, praw.clone()).numpy()
   np.savez_compressed(os.path.join(OUT, 'interp.npz'), **out)
+
+
+def _batch_octree(ids):
+  octs = []
+  for i in ids:
+    d = np.load(os.path.join(REF, 'test/data/octree/test_%03d.npz' % i))
+    pc = ocnn.octree.Points(torch.from_numpy(d['points']), torch.from_numpy(d['normals']))
+    o = ocnn.octree.Octree(d['depth'].item(), d['full_depth'].item())
+    o.build_octree(pc)
+    octs.append(o)
+  octree = ocnn.octree.merge_octrees(octs)
+  octree.construct_all_neigh()
+  return octree
+
+
+def extras():
+  """octree_avg_pool, octree_global_pool (octree_pool.py:68-124), octree_align (octree_align.py),
+  octree2voxel (octree2vox.py) of the reference on the merged octree 4+5."""
+  out = {}
+  octree = _batch_octree((4, 5))
+  other = _batch_octree((5, 4))          # same shapes in the other order: keys differ in the batch bits
+  g = torch.Generator().manual_seed(11)
+  C, depth = 5, 5
+  for ne in (False, True):
+    tag = '_ne' if ne else ''
+    n = int(octree.nnum_nempty[depth] if ne else octree.nnum[depth])
+    x = torch.randn(n, C, generator=g, requires_grad=True)
+    out['x' + tag] = x.detach().numpy()
+    for kernel, stride in (('222', 2), ('333', 2), ('333', 1)):
+      x.grad = None
+      y = ocnn.nn.octree_avg_pool(x, octree, depth, kernel, stride, ne)
+      gy = torch.randn(y.shape, generator=g)
+      y.backward(gy)
+      key = 'avg_%s_%d%s' % (kernel, stride, tag)
+      out[key], out[key + '_gy'], out[key + '_gx'] = y.detach().numpy(), gy.numpy(), x.grad.numpy().copy()
+    x.grad = None
+    y = ocnn.nn.octree_global_pool(x, octree, depth, ne)
+    gy = torch.randn(y.shape, generator=g)
+    y.backward(gy)
+    out['glob' + tag], out['glob%s_gy' % tag], out['glob%s_gx' % tag] = y.detach().numpy(), gy.numpy(), x.grad.numpy().copy()
+    x.grad = None
+    y = ocnn.nn.octree_align(x, octree, other, depth, ne)
+    gy = torch.randn(y.shape, generator=g)
+    y.backward(gy)
+    out['align' + tag], out['align%s_gy' % tag], out['align%s_gx' % tag] = y.detach().numpy(), gy.numpy(), x.grad.numpy().copy()
+  for ne in (False, True):
+    tag = '_ne' if ne else ''
+    d4 = 4
+    n = int(octree.nnum_nempty[d4] if ne else octree.nnum[d4])
+    x = torch.randn(n, 3, generator=g, requires_grad=True)
+    v = ocnn.nn.octree2voxel(x, octree, d4, ne)
+    gy = torch.randn(v.shape, generator=g)
+    v.backward(gy)
+    out['vox_x' + tag], out['vox' + tag], out['vox%s_gy' % tag], out['vox%s_gx' % tag] = \
+        x.detach().numpy(), v.detach().numpy(), gy.numpy(), x.grad.numpy().copy()
+  np.savez_compressed(os.path.join(OUT, 'extras.npz'), **out)
 
 
 def synthetic():
@@ -318,6 +376,7 @@ if __name__ == '__main__':
   hand3()
   ref_fixtures()
   interp()
+  extras()
   synthetic()
   for f in sorted(os.listdir(OUT)):
     if f.endswith('.npz'):

@@ -220,3 +220,41 @@ def test_search_and_interp_against_reference(golden):
       assert np.allclose(orc.linear_pts(dd, kk, depth, gp, bool(bc)), it['g_linear%s_bc%d' % (tag, bc)], atol=1e-5)
       assert np.allclose(orc.linear_pts_backward(gy, kk, depth, gp, dd.shape[0], bool(bc)),
                          it['g_linear%s_bc%d_grad' % (tag, bc)], atol=1e-5)
+
+
+def test_pool_align_voxel_against_reference(golden):
+  # octree_avg_pool / octree_global_pool / octree_align / octree2voxel on the merged octree 4+5
+  b45, ex = golden['batch45'], golden['extras']
+  depth, fd, B = int(b45['depth']), int(b45['full_depth']), 2
+  nnum = [int(v) for v in b45['nnum']]
+  offs = np.concatenate([[0], np.cumsum(nnum)])
+  keys = [b45['key'][offs[d]:offs[d + 1]] for d in range(depth + 1)]
+  child = [b45['child'][offs[d]:offs[d + 1]] for d in range(depth + 1)]
+  noffs = np.concatenate([[0], np.cumsum(nnum[1:])])
+  neigh = [None] + [b45['neigh'][noffs[d - 1]:noffs[d]] for d in range(1, depth + 1)]
+  d = 5
+  for ne in (False, True):
+    tag = '_ne' if ne else ''
+    x = ex['x' + tag]
+    for kernel, stride in (('222', 2), ('333', 2), ('333', 1)):
+      ng = orc.get_neigh(neigh[d], child[d], kernel, stride, ne)
+      key = 'avg_%s_%d%s' % (kernel, stride, tag)
+      y, _ = orc.avg_pool(x, ng)
+      assert np.allclose(y, ex[key], atol=1e-6), key
+      assert np.allclose(orc.avg_pool_backward(ex[key + '_gy'], ng, x.shape[0]), ex[key + '_gx'], atol=1e-6), key
+    kk = keys[d][child[d] >= 0] if ne else keys[d]
+    bid = (kk >> 48).astype(np.int64)
+    y, cnt = orc.global_pool(x, bid, B)
+    assert np.allclose(y, ex['glob' + tag], atol=1e-6)
+    assert np.allclose(orc.global_pool_backward(ex['glob%s_gy' % tag], bid, cnt), ex['glob%s_gx' % tag], atol=1e-7)
+    # the query octree holds the same two shapes in the other order: swap the batch bit of the keys
+    q = np.sort(kk ^ (np.int64(1) << 48))
+    y, idx = orc.align(x, kk, q)
+    assert np.allclose(y, ex['align' + tag], atol=0)
+    assert np.allclose(orc.nearest_pts_backward(ex['align%s_gy' % tag], idx, x.shape[0]), ex['align%s_gx' % tag], atol=1e-6)
+    d4 = 4
+    k4 = keys[d4][child[d4] >= 0] if ne else keys[d4]
+    xx, yy, zz, bb = orc.key2xyz(k4, d4)
+    v = orc.octree2voxel(ex['vox_x' + tag], xx, yy, zz, bb, d4, B)
+    assert np.array_equal(v, ex['vox' + tag])
+    assert np.array_equal(ex['vox%s_gy' % tag][bb, xx, yy, zz], ex['vox%s_gx' % tag])
