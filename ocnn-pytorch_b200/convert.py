@@ -42,6 +42,18 @@ def _swap_one(m: torch.nn.Module):
     return _nn.OctreeMaxPool(m.nempty, m.return_indices)
   if name == 'OctreeUpsample' and getattr(m, 'method', None) == 'nearest':
     return _nn.OctreeUpsample('nearest', m.nempty)
+  if name == 'OctreeMaxUnpool':
+    return _nn.OctreeMaxUnpool(m.nempty)
+  if name == 'OctreeGlobalPool':
+    return _nn.OctreeGlobalPool(m.nempty)
+  if name == 'OctreeAvgPool':
+    return _nn.OctreeAvgPool(m.kernel_size, m.stride, m.nempty)
+  if name == 'OctreeInterp':
+    return _nn.OctreeInterp(m.method, m.nempty, m.bound_check, m.rescale_pts)
+  if name == 'Octree2Voxel':
+    return _nn.Octree2Voxel(m.nempty)
+  if name in ('OctreeDropPath', 'DropPath'):
+    return _nn.OctreeDropPath(m.drop_prob, m.nempty, m.scale_by_keep)
   return None
 
 

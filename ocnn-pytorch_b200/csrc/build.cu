@@ -29,6 +29,7 @@ struct BuildLayout {
   size_t key_a, key_b, val_a, val_b, hist, scan_tmp, leaf_rank, leaf_start, counts;
   size_t level_keys;  // (depth - full_depth + 1) arrays of npts u64, index 0 = depth
   size_t level_pidx;  // (depth - full_depth) arrays of npts i32, index 0 = depth
+  size_t level_first; // (depth - full_depth) arrays of npts + 1 i32: first node of every parent, index 0 = depth
   size_t total;
   int64_t sort_blocks;
 };
@@ -53,6 +54,7 @@ static BuildLayout build_layout(int64_t npts, int depth, int full_depth) {
   const int nlev = depth - full_depth + 1;
   L.level_keys = take((size_t)nlev * P * 8);
   L.level_pidx = take((size_t)(nlev > 1 ? nlev - 1 : 1) * P * 4);
+  L.level_first = take((size_t)(nlev > 1 ? nlev - 1 : 1) * (P + 1) * 4);
   L.total = off;
   return L;
 }
@@ -204,10 +206,12 @@ struct ParentSink {
   const uint64_t* key;
   uint64_t* pkey;
   int32_t* pidx;
-  __device__ void operator()(int64_t i, int64_t, int flag, int ex) const {
+  int32_t* pfirst;   // pfirst[r] = first node of parent r, pfirst[#parents] = n
+  __device__ void operator()(int64_t i, int64_t n, int flag, int ex) const {
     const int r = ex + flag - 1;
     pidx[i] = r;
-    if (flag) pkey[r] = key[i] >> 3;
+    if (flag) { pkey[r] = key[i] >> 3; pfirst[r] = (int32_t)i; }
+    if (i == n - 1) pfirst[r + 1] = (int32_t)n;
   }
 };
 
@@ -243,20 +247,23 @@ __global__ void full_children_kernel(const uint64_t* __restrict__ lk, int64_t n,
     children[lk[i]] = (int32_t)i;
 }
 
-// keys of a sparse layer: node t is child (t & 7) of the (t >> 3)-th parent
-__global__ void level_keys_kernel(const uint64_t* __restrict__ pkeys, int64_t nnum, int depth,
-                                  int64_t* __restrict__ keys) {
+// A sparse layer in one pass: node t is child (t & 7) of the (t >> 3)-th non-empty parent; its
+// key follows from the parent's key, and it is non-empty if one of the parent's (at most 8,
+// key-sorted) nodes lk[first[p] .. first[p+1]) has that child index - its rank is the position.
+__global__ void level_emit_kernel(const uint64_t* __restrict__ pkeys, const uint64_t* __restrict__ lk,
+                                  const int32_t* __restrict__ first, int64_t nnum, int depth,
+                                  int64_t* __restrict__ keys, int32_t* __restrict__ children) {
   for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < nnum;
-       t += (int64_t)gridDim.x * blockDim.x)
-    keys[t] = expand_key((pkeys[t >> 3] << 3) | (uint64_t)(t & 7), depth);
-}
-
-__global__ void level_children_kernel(const uint64_t* __restrict__ lk,
-                                      const int32_t* __restrict__ pidx, int64_t n,
-                                      int32_t* __restrict__ children) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
-       i += (int64_t)gridDim.x * blockDim.x)
-    children[((int64_t)pidx[i] << 3) | (int64_t)(lk[i] & 7)] = (int32_t)i;
+       t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t p = t >> 3;
+    const uint64_t c = (uint64_t)(t & 7);
+    keys[t] = expand_key((pkeys[p] << 3) | c, depth);
+    int32_t child = -1;
+    const int32_t e = first[p + 1];
+    for (int32_t i = first[p]; i < e; ++i)
+      if ((lk[i] & 7) == c) child = i;
+    children[t] = child;
+  }
 }
 
 __global__ void point_rank_kernel(const uint32_t* __restrict__ perm,
@@ -425,7 +432,8 @@ extern "C" int oc_build_octree_count(const float* points, const void* batch_id, 
     const uint64_t* cur = lk + (size_t)(depth - d) * npts;
     uint64_t* par = lk + (size_t)(depth - d + 1) * npts;
     int32_t* pidx = lp + (size_t)(depth - d) * npts;
-    OC_CUDA_OK(device_scan(ParentHead{cur}, ParentSink{cur, par, pidx}, npts, counts + d, scan_tmp,
+    int32_t* pfirst = (int32_t*)(ws + L.level_first) + (size_t)(depth - d) * (npts + 1);
+    OC_CUDA_OK(device_scan(ParentHead{cur}, ParentSink{cur, par, pidx, pfirst}, npts, counts + d, scan_tmp,
                            counts + d - 1, s));
   }
   int64_t h_counts[32];
@@ -455,7 +463,7 @@ extern "C" int oc_build_octree_emit(const float* points, const float* normals, c
   const char* ws = (const char*)workspace;
   const uint32_t* perm = (const uint32_t*)(ws + L.val_a);
   const uint64_t* lk = (const uint64_t*)(ws + L.level_keys);
-  const int32_t* lp = (const int32_t*)(ws + L.level_pidx);
+  const int32_t* lf = (const int32_t*)(ws + L.level_first);
   const int32_t* leaf_rank = (const int32_t*)(ws + L.leaf_rank);
   const int32_t* leaf_start = (const int32_t*)(ws + L.leaf_start);
 
@@ -475,10 +483,10 @@ extern "C" int oc_build_octree_emit(const float* points, const float* normals, c
     const int64_t nnum = 8 * h_nnum_nempty[d - 1];
     const int64_t nne = h_nnum_nempty[d];
     OC_REQUIRE(h_keys[d] && h_children[d], OC_EINVAL, "emit: null output at depth %d", d);
-    level_keys_kernel<<<grid1d(nnum), 256, 0, s>>>(lk + (size_t)(depth - d + 1) * npts, nnum, d, h_keys[d]);
-    fill_i32_kernel<<<grid1d(nnum), 256, 0, s>>>(h_children[d], nnum, -1);
-    level_children_kernel<<<grid1d(nne), 256, 0, s>>>(lk + (size_t)(depth - d) * npts,
-                                                      lp + (size_t)(depth - d) * npts, nne, h_children[d]);
+    (void)nne;
+    level_emit_kernel<<<grid1d(nnum), 256, 0, s>>>(lk + (size_t)(depth - d + 1) * npts, lk + (size_t)(depth - d) * npts,
+                                                   lf + (size_t)(depth - d) * (npts + 1), nnum, d, h_keys[d],
+                                                   h_children[d]);
   }
   OC_LAUNCH_OK("octree emit kernels");
   if (out_idx) point_rank_kernel<<<grid1d(npts), 256, 0, s>>>(perm, leaf_rank, npts, out_idx);
