@@ -494,6 +494,15 @@ def run_suite(args, b200, octree, dev):
   dw = b200.nn.OctreeDWConv(C, [3]).to(dev)
   table, taps = octree.conv_table(D, '333', 1, False)
   emit('dwconv333_fwd C=256 fp16', _time(lambda: dw(x, octree, D)), nbytes=2 * n8 * C * s + n8 * 27 * 8, rows=n8)
+  xg = x.clone().requires_grad_()
+  gdw = torch.randn(n8, C, device=dev, generator=g).half()
+
+  def dw_step():
+    xg.grad = None
+    dw.weights.grad = None
+    dw(xg, octree, D).backward(gdw)
+  emit('dwconv333 fwd+bwd C=256 fp16', _time(dw_step), nbytes=3 * (2 * n8 * C * s + n8 * 27 * 8) + n8 * C * s, rows=n8)
+  del xg, gdw
   emit('maxpool_fwd C=256 fp16', _time(lambda: b200.nn.octree_max_pool(x, octree, D)),
        nbytes=(n8 + n7) * C * s + int(octree.nnum_nempty[D - 1]) * C * 8, rows=n8)
   xc = torch.randn(n7, C, device=dev, generator=g).half()
