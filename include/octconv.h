@@ -235,12 +235,20 @@ size_t oc_tile_table_bytes(int64_t n_out, int K);
 /* n_in > 0: number of feature rows the table indexes; an entry >= n_in is stored as -1 and
  * the next oc_status_check returns OC_EINVAL (the kernels do not re-check indices).  n_in = 0: no check.
  * The table holds an even number of blocks (a padding block of -1 if needed). */
+/* row_perm (device int32 (n_out), a permutation of 0 .. n_out-1, or NULL): position j of the tile
+ * table then holds table row row_perm[j].  Grouping rows that share their valid taps makes whole
+ * taps empty in a tile, and empty taps are skipped: the inverse table of a stride-2 convolution
+ * (oc_neigh_inverse) has 1 to 8 valid taps of 27 per row and which ones depends only on the
+ * node's child index, so rows ordered by child index run 3.4 instead of 27 taps per tile.
+ * The same array must be given to oc_conv_fwd_tiled; oc_conv_wgrad_tiled takes unpermuted tables. */
 int oc_tile_table_build(const void* table, int idx_bytes, int table_cols, const int* h_taps, int K,
-                        int64_t n_out, int64_t n_in, void* tiles, size_t tiles_bytes, void* stream);
-/* oc_conv_fwd with the table given as a tile table (same K and tap order as at build). */
+                        int64_t n_out, int64_t n_in, const int32_t* row_perm, void* tiles,
+                        size_t tiles_bytes, void* stream);
+/* oc_conv_fwd with the table given as a tile table (same K and tap order as at build; out[row_perm[j]]
+ * receives position j when the table was built with a row permutation). */
 int oc_conv_fwd_tiled(const void* data, int64_t n_in, const void* weights, int w_dtype,
-                      int w_transposed, const void* bias, const void* tiles, int K, int64_t n_out,
-                      int Cin, int Cout, int dtype, void* out, void* workspace,
+                      int w_transposed, const void* bias, const void* tiles, const int32_t* row_perm,
+                      int K, int64_t n_out, int Cin, int Cout, int dtype, void* out, void* workspace,
                       size_t workspace_bytes, void* stream);
 
 /* Weight gradient, ocnn/nn/octree_conv.py:170-202 (weight_gemm) and

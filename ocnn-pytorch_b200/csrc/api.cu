@@ -105,9 +105,9 @@ extern "C" size_t oc_conv_workspace_bytes(int K, int Cin, int Cout, int dtype) {
 // `tiles` non-null: the table comes as a tile table (tensor-core shapes only).
 static int conv_fwd_impl(const char* who, const void* data, int64_t n_in, const void* weights, int w_dtype,
                          int w_transposed, const void* bias, const void* table, int idx_bytes,
-                         int table_cols, const int* h_taps, const void* tiles, int K, int64_t n_out, int Cin,
-                         int Cout, int dtype, void* out, void* workspace, size_t workspace_bytes,
-                         void* stream) {
+                         int table_cols, const int* h_taps, const void* tiles, const int32_t* perm, int K,
+                         int64_t n_out, int Cin, int Cout, int dtype, void* out, void* workspace,
+                         size_t workspace_bytes, void* stream) {
   int rc = check_conv_common(who, K, Cin, Cout, dtype, idx_bytes, table_cols, n_in, n_out);
   if (rc) return rc;
   OC_REQUIRE(w_dtype == OC_F32 || w_dtype == dtype, OC_EINVAL, "%s: weights must be fp32 or the data dtype", who);
@@ -126,7 +126,7 @@ static int conv_fwd_impl(const char* who, const void* data, int64_t n_in, const 
              "%s: a tile table needs fp16/bf16 data and channel counts that are multiples of 16 "
              "(ask oc_conv_tiled_supported); use oc_conv_fwd with the plain table", who);
   OC_REQUIRE(workspace_bytes >= P.total, OC_ENOMEM, "%s: workspace %zu < %zu bytes", who, workspace_bytes, P.total);
-  a.data = data; a.n_in = n_in; a.bias = bias; a.table = table; a.tiled = tiles; a.idx_bytes = idx_bytes;
+  a.data = data; a.n_in = n_in; a.bias = bias; a.table = table; a.tiled = tiles; a.perm = perm; a.idx_bytes = idx_bytes;
   a.table_cols = table_cols; a.K = K; a.n_out = n_out; a.Cin = Cin; a.Cout = Cout; a.dtype = dtype;
   a.out = out;
   cudaStream_t s = (cudaStream_t)stream;
@@ -147,7 +147,7 @@ extern "C" int oc_conv_fwd(const void* data, int64_t n_in, const void* weights, 
                            int Cout, int dtype, void* out, void* workspace, size_t workspace_bytes,
                            void* stream) {
   return conv_fwd_impl("oc_conv_fwd", data, n_in, weights, w_dtype, w_transposed, bias, table, idx_bytes,
-                       table_cols, h_taps, nullptr, K, n_out, Cin, Cout, dtype, out, workspace,
+                       table_cols, h_taps, nullptr, nullptr, K, n_out, Cin, Cout, dtype, out, workspace,
                        workspace_bytes, stream);
 }
 
@@ -161,8 +161,8 @@ extern "C" size_t oc_tile_table_bytes(int64_t n_out, int K) {
 }
 
 extern "C" int oc_tile_table_build(const void* table, int idx_bytes, int table_cols, const int* h_taps,
-                                   int K, int64_t n_out, int64_t n_in, void* tiles, size_t tiles_bytes,
-                                   void* stream) {
+                                   int K, int64_t n_out, int64_t n_in, const int32_t* row_perm, void* tiles,
+                                   size_t tiles_bytes, void* stream) {
   OC_REQUIRE(K >= 1 && K <= OC_MAX_TAPS, OC_EINVAL, "oc_tile_table_build: K %d not in [1,27]", K);
   OC_REQUIRE(idx_bytes == 8 || idx_bytes == 4, OC_EINVAL, "oc_tile_table_build: idx_bytes must be 4 or 8");
   OC_REQUIRE(table_cols >= 1 && table_cols <= 27, OC_EINVAL, "oc_tile_table_build: table_cols %d not in [1,27]", table_cols);
@@ -176,17 +176,17 @@ extern "C" int oc_tile_table_build(const void* table, int idx_bytes, int table_c
   OC_REQUIRE(((uintptr_t)tiles % 16) == 0, OC_EINVAL, "oc_tile_table_build: tiles must be 16-byte aligned");
   OC_REQUIRE(tiles_bytes >= tile_table_bytes(n_out, K), OC_ENOMEM, "oc_tile_table_build: tiles %zu < %zu bytes",
              tiles_bytes, tile_table_bytes(n_out, K));
-  return launch_tile_table(table, idx_bytes, table_cols, taps, K, n_out, n_in, tiles, (cudaStream_t)stream);
+  return launch_tile_table(table, idx_bytes, table_cols, taps, K, n_out, n_in, row_perm, tiles, (cudaStream_t)stream);
 }
 
 extern "C" int oc_conv_fwd_tiled(const void* data, int64_t n_in, const void* weights, int w_dtype,
-                                 int w_transposed, const void* bias, const void* tiles, int K,
-                                 int64_t n_out, int Cin, int Cout, int dtype, void* out, void* workspace,
+                                 int w_transposed, const void* bias, const void* tiles, const int32_t* row_perm,
+                                 int K, int64_t n_out, int Cin, int Cout, int dtype, void* out, void* workspace,
                                  size_t workspace_bytes, void* stream) {
   OC_REQUIRE(tiles, OC_EINVAL, "oc_conv_fwd_tiled: null tile table");
   // no plain table: its width only has to pass the range check, the taps are 0 .. K-1
   return conv_fwd_impl("oc_conv_fwd_tiled", data, n_in, weights, w_dtype, w_transposed, bias, nullptr, 4,
-                       K >= 1 && K <= OC_MAX_TAPS ? K : 1, nullptr, tiles, K, n_out, Cin, Cout, dtype, out,
+                       K >= 1 && K <= OC_MAX_TAPS ? K : 1, nullptr, tiles, row_perm, K, n_out, Cin, Cout, dtype, out,
                        workspace, workspace_bytes, stream);
 }
 

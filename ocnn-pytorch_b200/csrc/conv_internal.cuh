@@ -10,6 +10,7 @@ struct ConvArgs {
   const void* bias;    // (Cout) or null, same dtype as data
   const void* table;   // (n_out, table_cols) indices into data rows, < 0 = none
   const void* tiled = nullptr;   // the same table as a tile table (tensor-core kernels only); then `table` may be null
+  const int32_t* perm = nullptr; // row order of the tile table (position -> output row), null = identity
   int idx_bytes;       // 8 or 4
   int table_cols;
   TapList taps;
@@ -48,7 +49,7 @@ bool conv_tc_supported(int K, int Cin, int Cout, int dtype);
 size_t tile_table_block_bytes(int K);
 size_t tile_table_bytes(int64_t n_out, int K);
 int launch_tile_table(const void* table, int idx_bytes, int table_cols, const TapList& taps, int K,
-                      int64_t n_out, int64_t n_in, void* out, cudaStream_t s);
+                      int64_t n_out, int64_t n_in, const int32_t* perm, void* out, cudaStream_t s);
 size_t conv_tc_weight_bytes(int K, int Cin, int Cout);
 int prep_weights_tc(const void* w, int w_dtype, int K, int Cin, int Cout, int transposed, int dtype,
                     void* out, cudaStream_t s);

@@ -83,6 +83,7 @@ struct Params {
   const void* bias;
   const void* table;
   const void* tiled;   // tile table (then `table` is unused) or null
+  const int32_t* perm; // tile-table position -> output row (null: identity); see oc_tile_table_build
   uint32_t tiled_block_bytes;
   void* out;
   int64_t n_out;
@@ -474,7 +475,8 @@ conv_tc_kernel(const Params p) {
       PROF_T(e1); PROF_ADD(0, e1 - e0);
 #pragma unroll
       for (int h = 0; h < H; ++h) {
-        const int64_t row = (tile * H + h) * TILE_M + warp * 32 + lane;
+        int64_t row = (tile * H + h) * TILE_M + warp * 32 + lane;     // position in the tile table
+        if (p.perm && row < p.n_out) row = p.perm[row];               // -> output row
         const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (acc * H + h) * (uint32_t)p.NT;
         for (int c0 = 0; c0 < p.NT; c0 += 16) {
           uint32_t r[16];
@@ -609,17 +611,18 @@ size_t tile_table_bytes(int64_t n_out, int K) { return (size_t)tile_table_blocks
 template <typename I>
 __global__ void __launch_bounds__(tc::TILE_M)
 tile_table_kernel(const I* __restrict__ table, int table_cols, TapList taps, int K, int64_t n_out, int64_t n_in,
-                  uint8_t* __restrict__ out, uint32_t block_bytes) {
+                  const int32_t* __restrict__ perm, uint8_t* __restrict__ out, uint32_t block_bytes) {
   __shared__ uint32_t smask;
   if (threadIdx.x == 0) smask = 0;
   __syncthreads();
   const int64_t tile = blockIdx.x;
-  const int64_t r = tile * tc::TILE_M + threadIdx.x;
+  const int64_t pos = tile * tc::TILE_M + threadIdx.x;        // position in the tile table
+  const int64_t r = (perm && pos < n_out) ? (int64_t)perm[pos] : pos;   // row of the plain table
   uint8_t* blk = out + (size_t)tile * block_bytes;
   int* rows = (int*)(blk + tc::IDX_HDR_BYTES);
   uint32_t m = 0;
   for (int k = 0; k < K; ++k) {
-    int64_t v64 = r < n_out ? (int64_t)table[r * table_cols + taps.t[k]] : -1;
+    int64_t v64 = pos < n_out ? (int64_t)table[r * table_cols + taps.t[k]] : -1;
     if (n_in > 0 && v64 >= n_in) {   // would read past the feature rows: dropped and reported
       v64 = -1;
       atomicMax(&g_tc_status, 90);
@@ -635,14 +638,14 @@ tile_table_kernel(const I* __restrict__ table, int table_cols, TapList taps, int
 }
 
 int launch_tile_table(const void* table, int idx_bytes, int table_cols, const TapList& taps, int K,
-                      int64_t n_out, int64_t n_in, void* out, cudaStream_t s) {
+                      int64_t n_out, int64_t n_in, const int32_t* perm, void* out, cudaStream_t s) {
   if (n_out == 0) return OC_OK;
   const unsigned grid = (unsigned)tile_table_blocks(n_out);   // a padding block holds -1 only
   const uint32_t bb = (uint32_t)tile_table_block_bytes(K);
   if (idx_bytes == 8)
-    tile_table_kernel<int64_t><<<grid, tc::TILE_M, 0, s>>>((const int64_t*)table, table_cols, taps, K, n_out, n_in, (uint8_t*)out, bb);
+    tile_table_kernel<int64_t><<<grid, tc::TILE_M, 0, s>>>((const int64_t*)table, table_cols, taps, K, n_out, n_in, perm, (uint8_t*)out, bb);
   else
-    tile_table_kernel<int32_t><<<grid, tc::TILE_M, 0, s>>>((const int32_t*)table, table_cols, taps, K, n_out, n_in, (uint8_t*)out, bb);
+    tile_table_kernel<int32_t><<<grid, tc::TILE_M, 0, s>>>((const int32_t*)table, table_cols, taps, K, n_out, n_in, perm, (uint8_t*)out, bb);
   OC_LAUNCH_OK("tile_table_kernel");
   return OC_OK;
 }
@@ -699,6 +702,7 @@ int launch_conv_tc(const ConvArgs& a, const void* Wimg, int* status_dev, cudaStr
   if (a.n_out == 0) return OC_OK;
   tc::Params prm;
   prm.data = a.data; prm.wimg = Wimg; prm.bias = a.bias; prm.table = a.table; prm.out = a.out;
+  prm.perm = a.tiled ? a.perm : nullptr;
   prm.tiled = a.tiled; prm.tiled_block_bytes = (uint32_t)tile_table_block_bytes(a.K);
   OC_REQUIRE(((uintptr_t)a.tiled % 16) == 0, OC_EINVAL, "conv_tc: the tile table must be 16-byte aligned");
   prm.n_out = a.n_out; prm.table_cols = a.table_cols; prm.K = a.K; prm.Cin = a.Cin; prm.Cout = a.Cout;

@@ -495,7 +495,7 @@ int launch_wgrad_tc(const WgradArgs& a, float* grad_w, void* workspace, size_t w
   const void* tiled = a.tiled;
   if (!tiled) {   // plain table: regroup it first (one pass over the table)
     void* tt = (char*)workspace + partial_bytes;
-    int rc = launch_tile_table(a.table, a.idx_bytes, a.table_cols, a.taps, a.K, a.n_out, a.n_in, tt, s);
+    int rc = launch_tile_table(a.table, a.idx_bytes, a.table_cols, a.taps, a.K, a.n_out, a.n_in, nullptr, tt, s);
     if (rc) return rc;
     tiled = tt;
   }

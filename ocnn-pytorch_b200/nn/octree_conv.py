@@ -27,17 +27,28 @@ def tiled_supported(K, c_in, c_out, dtype):
       bool(_lib.lib().oc_conv_tiled_supported(K, c_in, c_out, _lib.dtype_code(dtype)))
 
 
-def tile_table(table, taps, n_in=0):
+class TileTable:
+  r''' A tile table (uint8 tensor `tiles`) with the row order it was built in (`perm`, int32
+  positions -> table rows, or None for the natural order). '''
+
+  def __init__(self, tiles, perm=None):
+    self.tiles = tiles
+    self.perm = perm
+
+
+def tile_table(table, taps, n_in=0, perm=None):
   r''' Regroups columns `taps` of a neighbour table into blocks of 128 rows (16-byte
   header with the mask of non-empty taps, then one row of 128 int32 per tap): the form
   the tensor-core kernel fetches with one bulk copy per tile.  Returns a uint8 tensor.
   `n_in` > 0: the number of feature rows the table indexes; larger entries are dropped
-  and make the next ``_lib.status_check`` raise (the kernels trust the tile table). '''
+  and make the next ``_lib.status_check`` raise (the kernels trust the tile table).
+  `perm` (int32, a permutation of the rows): position j of the tile table holds row perm[j];
+  give the result to :func:`conv_gather` wrapped in a :class:`TileTable` with the same `perm`. '''
   _lib.require_cuda(table)
   K, n_out = len(taps), table.shape[0]
   tiles = torch.empty(_lib.lib().oc_tile_table_bytes(n_out, K), dtype=torch.uint8, device=table.device)
   _lib.call('oc_tile_table_build', _lib.ptr(table), _idx_bytes(table), table.shape[1],
-            _lib.int_array(taps), K, n_out, int(n_in), _lib.ptr(tiles), tiles.numel(),
+            _lib.int_array(taps), K, n_out, int(n_in), _lib.ptr(perm), _lib.ptr(tiles), tiles.numel(),
             _lib.stream(table.device))
   return tiles
 
@@ -62,9 +73,12 @@ def conv_gather(data, weights, w_transposed, bias, table, taps, c_in, c_out, til
   out = torch.empty(n_out, c_out, dtype=data.dtype, device=data.device)
   ws = _lib.workspace(_lib.lib().oc_conv_workspace_bytes(K, c_in, c_out, dt), data.device)
   if tiles is not None and n_out > 0 and tiled_supported(K, c_in, c_out, data.dtype):
+    perm = None
+    if isinstance(tiles, TileTable):
+      tiles, perm = tiles.tiles, tiles.perm
     _lib.call('oc_conv_fwd_tiled', _lib.ptr(data), data.shape[0], _lib.ptr(weights),
-              _lib.dtype_code(weights.dtype), int(w_transposed), _lib.ptr(bias), _lib.ptr(tiles), K,
-              n_out, c_in, c_out, dt, _lib.ptr(out), _lib.ptr(ws), ws.numel(),
+              _lib.dtype_code(weights.dtype), int(w_transposed), _lib.ptr(bias), _lib.ptr(tiles),
+              _lib.ptr(perm), K, n_out, c_in, c_out, dt, _lib.ptr(out), _lib.ptr(ws), ws.numel(),
               _lib.stream(data.device))
     return out
   _lib.call('oc_conv_fwd', _lib.ptr(data), data.shape[0], _lib.ptr(weights),
@@ -90,6 +104,9 @@ def conv_wgrad(data, grad_out, table, taps, c_in, c_out, want_bias_grad=False, t
   gb = torch.empty(c_out, dtype=torch.float32, device=data.device) if want_bias_grad else None
   ws = _lib.workspace(_lib.lib().oc_conv_wgrad_workspace_bytes(K, c_in, c_out, n_out, dt),
                       data.device)
+  if isinstance(tiles, TileTable):
+    assert tiles.perm is None, 'the weight gradient takes tile tables in the natural row order'
+    tiles = tiles.tiles
   if tiles is not None and n_out > 0 and tiled_supported(K, c_in, c_out, data.dtype):
     _lib.call('oc_conv_wgrad_tiled', _lib.ptr(data), data.shape[0], _lib.ptr(grad_out), n_out,
               _lib.ptr(tiles), K, c_in, c_out, dt, _lib.ptr(gw), _lib.ptr(gb), _lib.ptr(ws), ws.numel(),

@@ -160,15 +160,24 @@ def test_tile_table_layout_and_equivalence(mid_octree):
     tiles = octree.conv_tiles(d, kernel, stride, nempty, transposed)
     assert octree.conv_tiles(d, kernel, stride, nempty, transposed) is tiles      # cached
     K, n_out = len(taps), table.shape[0]
+    # the inverse table of a stride-2 convolution comes with its rows grouped by child index
+    grouped = transposed and stride == 2
+    assert isinstance(tiles, b200.nn.TileTable) == grouped
+    raw_t = tiles.tiles if grouped else tiles
+    order = to_np(tiles.perm).astype(np.int64) if grouped else np.arange(n_out)
+    if grouped:
+      assert np.array_equal(np.sort(order), np.arange(n_out))
+      cidx = to_np(octree.key(d, nempty) & 7)[order]
+      assert (np.diff(cidx) >= 0).all()                     # child index never decreases along the table
     nt = (n_out + 127) // 128
     nt = (nt + 1) // 2 * 2                  # padded to an even number of blocks
     blk = 16 + K * 512
-    assert tiles.dtype == torch.uint8 and tiles.numel() == nt * blk
-    raw = to_np(tiles).reshape(nt, blk)
+    assert raw_t.dtype == torch.uint8 and raw_t.numel() == nt * blk
+    raw = to_np(raw_t).reshape(nt, blk)
     hdr = raw[:, :16].copy().view(np.uint32)
     rows = raw[:, 16:].copy().view(np.int32).reshape(nt, K, 128)
     want = np.full((nt * 128, K), -1, np.int64)
-    want[:n_out] = to_np(table)[:, taps]
+    want[:n_out] = to_np(table)[:, taps][order]
     want = np.where(want < 0, -1, want).reshape(nt, 128, K).transpose(0, 2, 1)
     assert np.array_equal(rows, want)
     mask = ((want >= 0).any(axis=2) * (1 << np.arange(K))[None, :]).sum(axis=1)
@@ -274,6 +283,37 @@ def test_conv_packed_taps_all_kernel_shapes(mid_octree, cin, cout):
       assert_close(to_np(y), to_np(ref_y), TOL16, 'y %s' % kernel)
       assert torch.equal(y, yt)
       assert_close(to_np(gw), to_np(ref_gw), 2e-3, 'gw %s' % kernel)
+
+
+@pytest.mark.parametrize('nempty', [False, True])
+@pytest.mark.parametrize('kernel_size', [[3], [2]])
+def test_strided_conv_deconv_half_matches_fp32_path(mid_octree, kernel_size, nempty):
+  # Stride-2 conv and deconv on the tensor-core path (the input gradient of the conv and the forward
+  # of the deconv run on the inverse table with rows grouped by child index) against the fp32 kernels,
+  # which the golden tests pin to the reference.
+  octree, o = mid_octree
+  d = 6
+  g = torch.Generator(device=dev()).manual_seed(3)
+  n = int(o['nnum_nempty'][d] if nempty else o['nnum'][d])
+  x32 = torch.randn(n, 32, device=dev(), generator=g)
+  res = {}
+  for dtype in (torch.float32, torch.float16):
+    conv = b200.nn.OctreeConv(32, 64, kernel_size, 2, nempty).to(dev())
+    deconv = b200.nn.OctreeDeconv(64, 32, kernel_size, 2, nempty).to(dev())
+    gg = torch.Generator(device=dev()).manual_seed(4)
+    with torch.no_grad():
+      conv.weights.copy_(torch.randn(conv.weights.shape, device=dev(), generator=gg) * 0.05)
+      deconv.weights.copy_(torch.randn(deconv.weights.shape, device=dev(), generator=gg) * 0.05)
+    conv, deconv = conv.to(dtype), deconv.to(dtype)
+    x = x32.detach().to(dtype).clone().requires_grad_()
+    y = conv(x, octree, d)
+    z = deconv(y, octree, d - 1)
+    gz = torch.randn(z.shape, device=dev(), generator=gg).to(dtype)
+    z.backward(gz)
+    res[dtype] = [to_np(t) for t in (y, z, x.grad, conv.weights.grad, deconv.weights.grad)]
+  b200._lib.status_check(dev())
+  for a, b, name in zip(res[torch.float16], res[torch.float32], ('y', 'z', 'gx', 'gw_conv', 'gw_deconv')):
+    assert_close(a, b, TOL16, name)
 
 
 def test_conv_is_deterministic_and_linear(mid_octree):
