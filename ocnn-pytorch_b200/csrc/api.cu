@@ -197,7 +197,7 @@ extern "C" size_t oc_conv_wgrad_workspace_bytes(int K, int Cin, int Cout, int64_
 
 static int conv_wgrad_impl(const char* who, const void* data, int64_t n_in, const void* grad_out, int64_t n_out,
                            const void* table, int idx_bytes, int table_cols, const int* h_taps, const void* tiles,
-                           int K, int Cin, int Cout, int dtype, float* grad_w, float* grad_bias,
+                           const int32_t* perm, int K, int Cin, int Cout, int dtype, float* grad_w, float* grad_bias,
                            void* workspace, size_t workspace_bytes, void* stream) {
   int rc = check_conv_common(who, K, Cin, Cout, dtype, idx_bytes, table_cols, n_in, n_out);
   if (rc) return rc;
@@ -222,7 +222,7 @@ static int conv_wgrad_impl(const char* who, const void* data, int64_t n_in, cons
              "%s: a tile table needs fp16/bf16 data and channel counts that are multiples of 16 "
              "(ask oc_conv_tiled_supported); use oc_conv_wgrad with the plain table", who);
   OC_REQUIRE(workspace_bytes >= P.total, OC_ENOMEM, "%s: workspace %zu < %zu bytes", who, workspace_bytes, P.total);
-  a.data = data; a.n_in = n_in; a.grad_out = grad_out; a.n_out = n_out; a.table = table; a.tiled = tiles;
+  a.data = data; a.n_in = n_in; a.grad_out = grad_out; a.n_out = n_out; a.table = table; a.tiled = tiles; a.perm = perm;
   a.idx_bytes = idx_bytes; a.table_cols = table_cols; a.K = K; a.Cin = Cin; a.Cout = Cout; a.dtype = dtype;
   char* ws = (char*)workspace;
   if (P.tc) {
@@ -244,14 +244,15 @@ extern "C" int oc_conv_wgrad(const void* data, int64_t n_in, const void* grad_ou
                              int K, int Cin, int Cout, int dtype, float* grad_w, float* grad_bias,
                              void* workspace, size_t workspace_bytes, void* stream) {
   return conv_wgrad_impl("oc_conv_wgrad", data, n_in, grad_out, n_out, table, idx_bytes, table_cols, h_taps,
-                         nullptr, K, Cin, Cout, dtype, grad_w, grad_bias, workspace, workspace_bytes, stream);
+                         nullptr, nullptr, K, Cin, Cout, dtype, grad_w, grad_bias, workspace, workspace_bytes, stream);
 }
 
 extern "C" int oc_conv_wgrad_tiled(const void* data, int64_t n_in, const void* grad_out, int64_t n_out,
-                                   const void* tiles, int K, int Cin, int Cout, int dtype, float* grad_w,
-                                   float* grad_bias, void* workspace, size_t workspace_bytes, void* stream) {
+                                   const void* tiles, const int32_t* row_perm, int K, int Cin, int Cout, int dtype,
+                                   float* grad_w, float* grad_bias, void* workspace, size_t workspace_bytes,
+                                   void* stream) {
   OC_REQUIRE(tiles, OC_EINVAL, "oc_conv_wgrad_tiled: null tile table");
   return conv_wgrad_impl("oc_conv_wgrad_tiled", data, n_in, grad_out, n_out, nullptr, 4,
-                         K >= 1 && K <= OC_MAX_TAPS ? K : 1, nullptr, tiles, K, Cin, Cout, dtype, grad_w,
+                         K >= 1 && K <= OC_MAX_TAPS ? K : 1, nullptr, tiles, row_perm, K, Cin, Cout, dtype, grad_w,
                          grad_bias, workspace, workspace_bytes, stream);
 }

@@ -28,6 +28,7 @@ struct WgradArgs {
   int64_t n_out;
   const void* table;
   const void* tiled = nullptr;   // the same table as a tile table (tensor-core kernel only); then `table` may be null
+  const int32_t* perm = nullptr; // row order of the tile table (position -> row of grad_out), null = identity
   int idx_bytes;
   int table_cols;
   TapList taps;

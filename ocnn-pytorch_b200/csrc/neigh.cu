@@ -116,6 +116,18 @@ neigh_from_parent_kernel(const int64_t* __restrict__ neigh_p, const int32_t* __r
   }
 }
 
+// masks[r] = bit k set iff table[r, taps[k]] >= 0
+template <typename I>
+__global__ void tap_mask_kernel(const I* __restrict__ table, int table_cols, TapList taps, int K, int64_t n_rows,
+                                int32_t* __restrict__ masks) {
+  for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < n_rows; r += (int64_t)gridDim.x * blockDim.x) {
+    const I* row = table + r * table_cols;
+    uint32_t m = 0;
+    for (int k = 0; k < K; ++k) m |= (row[taps.t[k]] >= 0 ? 1u : 0u) << k;
+    masks[r] = (int32_t)m;
+  }
+}
+
 struct NemptyFlag {
   const int32_t* children;
   __device__ int operator()(int64_t i, int64_t) const { return children[i] >= 0 ? 1 : 0; }
@@ -222,6 +234,25 @@ extern "C" int oc_neigh_from_parent(const int64_t* neigh_p, const int32_t* child
   if (blocks > cap) blocks = cap;
   neigh_from_parent_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(neigh_p, children_p, nnum_p, neigh, neigh32);
   OC_LAUNCH_OK("neigh_from_parent_kernel");
+  return OC_OK;
+}
+
+extern "C" int oc_tap_masks(const void* table, int idx_bytes, int table_cols, const int* h_taps, int K,
+                            int64_t n_rows, int32_t* masks, void* stream) {
+  OC_REQUIRE(idx_bytes == 8 || idx_bytes == 4, OC_EINVAL, "oc_tap_masks: idx_bytes must be 4 or 8");
+  OC_REQUIRE(table_cols >= 1 && table_cols <= 27 && K >= 1 && K <= OC_MAX_TAPS && n_rows >= 0, OC_EINVAL,
+             "oc_tap_masks: bad sizes");
+  TapList taps;
+  int rc = make_taps(h_taps, K, table_cols, &taps, "oc_tap_masks");
+  if (rc) return rc;
+  if (n_rows == 0) return OC_OK;
+  OC_REQUIRE(table && masks, OC_EINVAL, "oc_tap_masks: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (idx_bytes == 8)
+    tap_mask_kernel<int64_t><<<grid1d(n_rows), 256, 0, s>>>((const int64_t*)table, table_cols, taps, K, n_rows, masks);
+  else
+    tap_mask_kernel<int32_t><<<grid1d(n_rows), 256, 0, s>>>((const int32_t*)table, table_cols, taps, K, n_rows, masks);
+  OC_LAUNCH_OK("tap_mask_kernel");
   return OC_OK;
 }
 

@@ -50,6 +50,7 @@ struct Params {
   const void* data;
   const void* gout;
   const void* tiled;    // tile table of the K taps
+  const int32_t* perm;  // tile-table position -> row of grad_out (null: identity)
   uint32_t tiled_block_bytes;
   float* partial;       // [row slices][K][Cin][Cout]
   int64_t n_out;
@@ -77,7 +78,7 @@ __host__ __device__ inline SmemLayout smem_layout(int GB, int stages) {
   L.bars = L.sidx + 2 * IDX_BUF_BYTES;
   L.hdr = L.bars + (2 * MAX_STAGES + 9) * 8;
   L.misc = L.hdr + MAX_STAGES * 4;
-  L.total = L.misc + 128;
+  L.total = L.misc + 128 + TILE_R * 4;            // + one tile's row order, staged by the loader warp
   return L;
 }
 
@@ -281,6 +282,7 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
     const uint8_t* gout = (const uint8_t*)p.gout;
     const uint32_t grow_bytes = (uint32_t)p.Cout * 2;
     const int chunk = lane & 7, rsub = lane >> 3;
+    volatile int32_t* sperm = (volatile int32_t*)(smem + L.misc + 128);
     uint32_t it = 0;
     for (int64_t tile = t_begin; tile < t_end; ++tile, ++it) {
       const int b = (int)(it & 1u);
@@ -291,6 +293,15 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
                  ifull_bar(b));
       }
       if (!mbar_wait(gempty_bar(b), ((it >> 1) & 1u) ^ 1u, abort_flag, &g_tc_status, 11)) break;
+      if (p.perm) {     // the tile's 128 rows of grad_out: one coalesced read, then from shared memory
+        __syncwarp();
+#pragma unroll
+        for (int q = 0; q < TILE_R / 32; ++q) {
+          const int64_t pos = tile * TILE_R + q * 32 + lane;
+          sperm[q * 32 + lane] = pos < p.n_out ? p.perm[pos] : 0;
+        }
+        __syncwarp();
+      }
       const uint32_t g_dst = s_base + L.gbuf + b * (uint32_t)(p.GB * BLK_BYTES);
       for (int gb = 0; gb < p.GB; ++gb) {
         const int col = n0 + gb * 64 + chunk * 8;
@@ -298,8 +309,9 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
 #pragma unroll 8
         for (int i = 0; i < TILE_R / 4; ++i) {
           const int r = 4 * i + rsub;
-          const int64_t grow = tile * TILE_R + r;
+          int64_t grow = tile * TILE_R + r;                 // position in the tile table
           const bool v = col_ok && grow < p.n_out;
+          if (v && p.perm) grow = sperm[r];                 // -> row of grad_out
           cp_async_16(g_dst + gb * BLK_BYTES + r * 128 + ((chunk ^ (r & 7)) << 4),
                       v ? gout + (size_t)grow * grow_bytes + (size_t)col * 2 : gout, v ? 16u : 0u);
         }
@@ -500,7 +512,7 @@ int launch_wgrad_tc(const WgradArgs& a, float* grad_w, void* workspace, size_t w
     tiled = tt;
   }
   wg::Params prm;
-  prm.data = a.data; prm.gout = a.grad_out; prm.tiled = tiled;
+  prm.data = a.data; prm.gout = a.grad_out; prm.tiled = tiled; prm.perm = a.tiled ? a.perm : nullptr;
   prm.tiled_block_bytes = (uint32_t)tile_table_block_bytes(a.K); prm.partial = (float*)workspace;
   prm.n_out = a.n_out; prm.tiles_per_slice = P.tiles_per_slice;
   prm.K = a.K; prm.Cin = a.Cin; prm.Cout = a.Cout; prm.KB = P.KB; prm.PACK = P.PACK; prm.nblk = P.nblk; prm.NTW = P.NTW;

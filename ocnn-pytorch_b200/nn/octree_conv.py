@@ -36,6 +36,18 @@ class TileTable:
     self.perm = perm
 
 
+def tap_mask_order(table, taps):
+  r''' Rows of `table` sorted (stably) by the bit mask of their valid taps, as an int32
+  permutation.  Tiles of a tile table built in this order hold rows with the same few taps,
+  and the kernels skip the taps that are empty in a whole tile. '''
+  _lib.require_cuda(table)
+  n = table.shape[0]
+  masks = torch.empty(n, dtype=torch.int32, device=table.device)
+  _lib.call('oc_tap_masks', _lib.ptr(table), _idx_bytes(table), table.shape[1], _lib.int_array(taps), len(taps), n,
+            _lib.ptr(masks), _lib.stream(table.device))
+  return torch.sort(masks, stable=True)[1].to(torch.int32).contiguous()
+
+
 def tile_table(table, taps, n_in=0, perm=None):
   r''' Regroups columns `taps` of a neighbour table into blocks of 128 rows (16-byte
   header with the mask of non-empty taps, then one row of 128 int32 per tap): the form
@@ -104,12 +116,12 @@ def conv_wgrad(data, grad_out, table, taps, c_in, c_out, want_bias_grad=False, t
   gb = torch.empty(c_out, dtype=torch.float32, device=data.device) if want_bias_grad else None
   ws = _lib.workspace(_lib.lib().oc_conv_wgrad_workspace_bytes(K, c_in, c_out, n_out, dt),
                       data.device)
+  perm = None
   if isinstance(tiles, TileTable):
-    assert tiles.perm is None, 'the weight gradient takes tile tables in the natural row order'
-    tiles = tiles.tiles
+    tiles, perm = tiles.tiles, tiles.perm
   if tiles is not None and n_out > 0 and tiled_supported(K, c_in, c_out, data.dtype):
     _lib.call('oc_conv_wgrad_tiled', _lib.ptr(data), data.shape[0], _lib.ptr(grad_out), n_out,
-              _lib.ptr(tiles), K, c_in, c_out, dt, _lib.ptr(gw), _lib.ptr(gb), _lib.ptr(ws), ws.numel(),
+              _lib.ptr(tiles), _lib.ptr(perm), K, c_in, c_out, dt, _lib.ptr(gw), _lib.ptr(gb), _lib.ptr(ws), ws.numel(),
               _lib.stream(data.device))
     return gw, gb
   _lib.call('oc_conv_wgrad', _lib.ptr(data), data.shape[0], _lib.ptr(grad_out), n_out,
@@ -178,12 +190,12 @@ class _OctreeDeconv(OctreeConvBase):
   def is_conv_layer(self): return False
 
 
-def _tiles(octree, depth, kernel, stride, nempty, transposed, K, c_in, c_out, data):
+def _tiles(octree, depth, kernel, stride, nempty, transposed, K, c_in, c_out, data, by_mask=True):
   r''' The octree's cached tile table of this convolution, or None where the
   tensor-core kernel does not apply (then the plain table is used). '''
   if not tiled_supported(K, c_in, c_out, data.dtype):
     return None
-  return octree.conv_tiles(depth, kernel, stride, nempty, transposed)
+  return octree.conv_tiles(depth, kernel, stride, nempty, transposed, by_mask)
 
 
 class OctreeConvFunction(Function):
@@ -216,7 +228,7 @@ class OctreeConvFunction(Function):
       grad_in = conv_gather(grad, weights, True, None, table_t, taps_t, cout, cin, tiles)
     if ctx.needs_input_grad[1] or (has_bias and ctx.needs_input_grad[2]):
       table, taps = octree.conv_table(depth, kernel, stride, nempty)
-      tiles = _tiles(octree, depth, kernel, stride, nempty, False, len(taps), cin, cout, data)
+      tiles = _tiles(octree, depth, kernel, stride, nempty, False, len(taps), cin, cout, data, by_mask=False)
       gw, gb = conv_wgrad(data, grad, table, taps, cin, cout, has_bias and ctx.needs_input_grad[2], tiles)
       grad_w = gw.to(weights.dtype) if ctx.needs_input_grad[1] else None
       grad_b = gb
@@ -254,7 +266,7 @@ class OctreeDeconvFunction(Function):
       grad_in = conv_gather(grad, weights, False, None, table, taps, cout, cin, tiles)
     if ctx.needs_input_grad[1]:
       # weights are (K, out_channels, in_channels): gathered operand = grad
-      tiles = _tiles(octree, nd, kernel, stride, nempty, False, len(taps), cout, cin, grad)
+      tiles = _tiles(octree, nd, kernel, stride, nempty, False, len(taps), cout, cin, grad, by_mask=False)
       gw, _ = conv_wgrad(grad, data, table, taps, cout, cin, False, tiles)
       grad_w = gw.to(weights.dtype)
     if has_bias and ctx.needs_input_grad[2]:

@@ -391,26 +391,26 @@ class Octree:
       self._table_cache[key] = inv
     return self._table_cache[key], list(range(len(taps)))
 
-  def conv_tiles(self, depth: int, kernel: str, stride: int, nempty: bool, transposed: bool = False):
+  def conv_tiles(self, depth: int, kernel: str, stride: int, nempty: bool, transposed: bool = False,
+                 by_mask: bool = True):
     r''' The table of :meth:`conv_table` (or :meth:`conv_table_transposed`) as a tile
-    table for the tensor-core convolution kernel, built once and cached like the
-    neighbour tables themselves.  The inverse table of a stride-2 convolution is built with
-    its rows grouped by child index (the valid taps of a row depend only on it), so that most
-    taps of a tile are empty and skipped; the result then carries the row order. '''
-    key = ('tiles', depth, kernel, stride, nempty, transposed)
+    table for the tensor-core convolution kernels, built once and cached like the
+    neighbour tables themselves.  Its rows are ordered by the bit mask of their valid taps
+    (:func:`tap_mask_order`): a tile then holds rows with the same few taps and the empty taps
+    are skipped - for the inverse table of a stride-2 convolution this groups the rows by child
+    index.  The result carries the row order (:class:`TileTable`).  ``by_mask=False`` keeps the
+    natural row order, which the weight-gradient kernel prefers (it pairs taps, so fewer of its
+    stages vanish, and it reads grad_out rows in table order). '''
+    key = ('tiles', depth, kernel, stride, nempty, transposed, by_mask)
     if key not in self._table_cache:
-      from ..nn.octree_conv import tile_table, TileTable
+      from ..nn.octree_conv import tile_table, tap_mask_order, TileTable
       table, taps = (self.conv_table_transposed if transposed else self.conv_table)(depth, kernel, stride, nempty)
-      perm = None
       if transposed and stride == 2:     # the inverse table indexes the rows of the forward table
         n_in = self.conv_table(depth, kernel, stride, nempty)[0].shape[0]
-        child_index = self.key(depth, nempty) & 7
-        perm = torch.sort(child_index, stable=True)[1].to(torch.int32).contiguous()
-        assert perm.numel() == table.shape[0]
       else:
         n_in = int(self.nnum_nempty[depth] if nempty else self.nnum[depth])
-      tiles = tile_table(table, taps, n_in, perm)
-      self._table_cache[key] = tiles if perm is None else TileTable(tiles, perm)
+      perm = tap_mask_order(table, taps) if by_mask else None
+      self._table_cache[key] = TileTable(tile_table(table, taps, n_in, perm), perm)
     return self._table_cache[key]
 
   def batch_offsets(self, depth: int, nempty: bool = False):

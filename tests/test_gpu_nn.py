@@ -160,15 +160,19 @@ def test_tile_table_layout_and_equivalence(mid_octree):
     tiles = octree.conv_tiles(d, kernel, stride, nempty, transposed)
     assert octree.conv_tiles(d, kernel, stride, nempty, transposed) is tiles      # cached
     K, n_out = len(taps), table.shape[0]
-    # the inverse table of a stride-2 convolution comes with its rows grouped by child index
-    grouped = transposed and stride == 2
-    assert isinstance(tiles, b200.nn.TileTable) == grouped
-    raw_t = tiles.tiles if grouped else tiles
-    order = to_np(tiles.perm).astype(np.int64) if grouped else np.arange(n_out)
-    if grouped:
-      assert np.array_equal(np.sort(order), np.arange(n_out))
-      cidx = to_np(octree.key(d, nempty) & 7)[order]
-      assert (np.diff(cidx) >= 0).all()                     # child index never decreases along the table
+    # the octree's tile tables come with their rows sorted by the mask of valid taps
+    assert isinstance(tiles, b200.nn.TileTable)
+    raw_t = tiles.tiles
+    order = to_np(tiles.perm).astype(np.int64)
+    assert np.array_equal(np.sort(order), np.arange(n_out))
+    row_mask = ((to_np(table)[:, taps] >= 0) * (1 << np.arange(K))[None, :]).sum(axis=1)
+    assert (np.diff(row_mask[order]) >= 0).all()                 # mask never decreases along the table
+    if transposed and stride == 2:
+      cidx = to_np(octree.key(d, nempty) & 7)[order]              # which groups the rows by child index
+      assert len(np.unique(cidx[:-1] != cidx[1:], return_counts=True)[1]) <= 2 and (cidx[:-1] != cidx[1:]).sum() < 64
+    # a table built in the natural order gives the same results
+    plain_tiles = b200.nn.tile_table(table, taps)
+    assert plain_tiles.dtype == torch.uint8
     nt = (n_out + 127) // 128
     nt = (nt + 1) // 2 * 2                  # padded to an even number of blocks
     blk = 16 + K * 512
@@ -191,7 +195,8 @@ def test_tile_table_layout_and_equivalence(mid_octree):
       bias = torch.randn(cout, device=dev(), generator=g).to(dtype)
       y_plain = b200.nn.conv_gather(x, w, False, bias, table, taps, cin, cout)
       y_tiled = b200.nn.conv_gather(x, w, False, bias, table, taps, cin, cout, tiles=tiles)
-      assert torch.equal(y_plain, y_tiled)
+      y_nat = b200.nn.conv_gather(x, w, False, bias, table, taps, cin, cout, tiles=plain_tiles)
+      assert torch.equal(y_plain, y_tiled) and torch.equal(y_plain, y_nat)
   b200._lib.status_check(dev())
   # an index past the feature rows is dropped while the tile table is built, and reported
   table, taps = octree.conv_table(6, '333', 1, False)
