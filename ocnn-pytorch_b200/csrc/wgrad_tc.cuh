@@ -16,8 +16,9 @@
 // group with at least one valid neighbour, gathers the two blocks and issues
 // 8 MMAs (K = 16 rows each) into that M tile's own TMEM accumulator, which stays
 // resident for the whole slice.
-// Roles: a loader warp brings in, per row tile, the tile-table block (one bulk copy) and
-// the grad_out tile; eight producer warps gather, each owning whole 64-channel blocks
+// Roles: a loader warp brings in, per row tile, the tile-table block (one bulk copy); four
+// warps load the grad_out tile, a quarter each (with one warp this load bounds the kernel when
+// Cout >= 128); eight producer warps gather, each owning whole 64-channel blocks
 // dealt round-robin (so a warp keeps a block of its own in flight while the others work
 // on theirs); one warp issues the MMAs.  The neighbour table always comes as a tile table
 // (oc_tile_table_build); the entry point builds one in the workspace when given a plain table.  At the end every accumulator is written to a
@@ -37,12 +38,14 @@ constexpr int TILE_R = 128;               // rows (the MMA K extent) per tile
 constexpr int BLK_BYTES = TILE_R * 128;   // one 64-channel block of 128 rows
 constexpr int PROD_WARPS = 8;
 constexpr int PROD_THREADS = PROD_WARPS * 32;
-// Warps 0-3: no main-loop role (epilogue at the end); warp 4: MMA issuer; producers: warps > 4
-// whose index is not a multiple of 4, so that the MMA warp's SM sub-partition holds no producer.
+// Warp 4: MMA issuer; warp 8: tile-table loader; producers: warps > 4 whose index is not a
+// multiple of 4, so that the MMA warp's SM sub-partition holds no copying warp; warps 1-3 and 15
+// load the grad_out tile (a quarter each); warps 0-11 run the epilogue at the end.
 constexpr int MMA_WARP = 4;
 constexpr int LOADER_WARP = 8;
 constexpr int N_WARPS = 5 + PROD_WARPS + (PROD_WARPS + 2) / 3;
 constexpr int THREADS = N_WARPS * 32;
+static_assert(N_WARPS == 16, "warp roles are laid out for 16 warps");
 constexpr int MAX_STAGES = 6;
 constexpr int MAX_MT = 16;                // M tiles (accumulators) per CTA
 
@@ -78,7 +81,7 @@ __host__ __device__ inline SmemLayout smem_layout(int GB, int stages) {
   L.bars = L.sidx + 2 * IDX_BUF_BYTES;
   L.hdr = L.bars + (2 * MAX_STAGES + 9) * 8;
   L.misc = L.hdr + MAX_STAGES * 4;
-  L.total = L.misc + 128 + TILE_R * 4;            // + one tile's row order, staged by the loader warp
+  L.total = L.misc + 128;
   return L;
 }
 
@@ -109,8 +112,9 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
   const int m_cnt = min(p.mt_per_cta, n_mt_all - m_lo);
   const int n0 = blockIdx.z * p.NTW;
   const int64_t n_tiles = (p.n_out + TILE_R - 1) / TILE_R;
-  const int64_t t_begin = (int64_t)slice * p.tiles_per_slice;
-  const int64_t t_end = min(n_tiles, t_begin + p.tiles_per_slice);
+  // slice s walks tiles s, s + slices, s + 2 slices, ...: equal work per slice whatever the
+  // row order of the tile table (tiles ordered by tap mask get more expensive towards the end)
+  const int64_t t_begin = slice, t_end = n_tiles, t_step = gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -118,7 +122,7 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
       mbar_init(empty_bar(s), 1);
     }
     for (int g = 0; g < 2; ++g) {
-      mbar_init(gfull_bar(g), 32);      // the lanes of the loader warp
+      mbar_init(gfull_bar(g), 128);     // the lanes of the four grad_out loader warps
       mbar_init(gempty_bar(g), 1);
       mbar_init(ifull_bar(g), 1);
       mbar_init(iempty_bar(g), PROD_WARPS);
@@ -138,6 +142,7 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
   const uint32_t tmem_base = misc[0];
 
   const int pw_raw = (warp - 5) - ((warp - 5) >> 2);
+  const int gq = warp == 15 ? 0 : (warp >= 1 && warp <= 3 ? warp : -1);   // quarter of the grad_out tile this warp loads
   if (warp > 4 && (warp & 3) != 0 && pw_raw < PROD_WARPS) {
     // ===================================================================== producers
     const int pw = pw_raw;
@@ -198,7 +203,7 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
     };
 
     uint32_t it = 0;
-    for (int64_t tile = t_begin; tile < t_end && ok; ++tile, ++it) {
+    for (int64_t tile = t_begin; tile < t_end && ok; tile += t_step, ++it) {
       const int buf = (int)(it & 1u);
       if (!mbar_wait(ifull_bar(buf), (it >> 1) & 1u, abort_flag, &g_tc_status, 14)) { ok = false; break; }
       const uint32_t mask_all = *(volatile uint32_t*)(smem + L.sidx + buf * IDX_BUF_BYTES);
@@ -275,16 +280,11 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
     if (bad_index) atomicMax(&g_tc_status, 90);
     cp_async_wait_all();
   } else if (warp == LOADER_WARP) {
-    // ===================================================================== loader
-    // Per row tile: the tile-table block (one bulk copy, lane 0) and the grad_out tile
-    // (dense rows, NTW columns, as GB swizzled 64-column blocks; 8 lanes per row).
+    // ===================================================================== index loader
+    // Per row tile: the tile-table block, one bulk copy issued by lane 0.
     const uint8_t* src = (const uint8_t*)p.tiled;
-    const uint8_t* gout = (const uint8_t*)p.gout;
-    const uint32_t grow_bytes = (uint32_t)p.Cout * 2;
-    const int chunk = lane & 7, rsub = lane >> 3;
-    volatile int32_t* sperm = (volatile int32_t*)(smem + L.misc + 128);
     uint32_t it = 0;
-    for (int64_t tile = t_begin; tile < t_end; ++tile, ++it) {
+    for (int64_t tile = t_begin; tile < t_end; tile += t_step, ++it) {
       const int b = (int)(it & 1u);
       if (it >= 2 && !mbar_wait(iempty_bar(b), ((it >> 1) - 1u) & 1u, abort_flag, &g_tc_status, 10)) break;
       if (lane == 0) {
@@ -292,28 +292,35 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
         bulk_g2s(s_base + L.sidx + b * IDX_BUF_BYTES, src + (size_t)tile * p.tiled_block_bytes, p.tiled_block_bytes,
                  ifull_bar(b));
       }
+      __syncwarp();
+    }
+  } else if (gq >= 0) {
+    // ===================================================================== grad_out loaders
+    // Four warps, each 32 rows of the tile: dense rows, NTW columns, as GB swizzled 64-column
+    // blocks; 8 lanes copy one row.  Lane l first reads which row of grad_out stands at
+    // position 32 gq + l of the tile (the row order of the tile table, or the position itself).
+    const uint8_t* gout = (const uint8_t*)p.gout;
+    const uint32_t grow_bytes = (uint32_t)p.Cout * 2;
+    const int chunk = lane & 7, rsub = lane >> 3;
+    uint32_t it = 0;
+    for (int64_t tile = t_begin; tile < t_end; tile += t_step, ++it) {
+      const int b = (int)(it & 1u);
+      const int64_t pos = tile * TILE_R + gq * 32 + lane;
+      int my_row = -1;
+      if (pos < p.n_out) my_row = p.perm ? p.perm[pos] : (int)pos;
       if (!mbar_wait(gempty_bar(b), ((it >> 1) & 1u) ^ 1u, abort_flag, &g_tc_status, 11)) break;
-      if (p.perm) {     // the tile's 128 rows of grad_out: one coalesced read, then from shared memory
-        __syncwarp();
-#pragma unroll
-        for (int q = 0; q < TILE_R / 32; ++q) {
-          const int64_t pos = tile * TILE_R + q * 32 + lane;
-          sperm[q * 32 + lane] = pos < p.n_out ? p.perm[pos] : 0;
-        }
-        __syncwarp();
-      }
-      const uint32_t g_dst = s_base + L.gbuf + b * (uint32_t)(p.GB * BLK_BYTES);
+      const uint32_t g_dst = s_base + L.gbuf + b * (uint32_t)(p.GB * BLK_BYTES) + (uint32_t)gq * 32u * 128u;
       for (int gb = 0; gb < p.GB; ++gb) {
         const int col = n0 + gb * 64 + chunk * 8;
         const bool col_ok = col < p.Cout && gb * 64 + chunk * 8 < p.NTW;
-#pragma unroll 8
-        for (int i = 0; i < TILE_R / 4; ++i) {
-          const int r = 4 * i + rsub;
-          int64_t grow = tile * TILE_R + r;                 // position in the tile table
-          const bool v = col_ok && grow < p.n_out;
-          if (v && p.perm) grow = sperm[r];                 // -> row of grad_out
+        const uint8_t* col_src = gout + (size_t)col * 2;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = 4 * i + rsub;                       // row of this warp's quarter
+          const int row = __shfl_sync(0xffffffffu, my_row, r);
+          const bool v = col_ok && row >= 0;
           cp_async_16(g_dst + gb * BLK_BYTES + r * 128 + ((chunk ^ (r & 7)) << 4),
-                      v ? gout + (size_t)grow * grow_bytes + (size_t)col * 2 : gout, v ? 16u : 0u);
+                      v ? col_src + (size_t)row * grow_bytes : gout, v ? 16u : 0u);
         }
       }
       cp_async_arrive_noinc(gfull_bar(b));
@@ -498,6 +505,7 @@ static int launch_wgrad_tc_t(const wg::Params& prm, const wg::Plan& P, cudaStrea
 int launch_wgrad_tc(const WgradArgs& a, float* grad_w, void* workspace, size_t workspace_bytes, cudaStream_t s) {
   const wg::Plan P = wg::make_plan(a.K, a.Cin, a.Cout, a.n_out, a.dtype);
   OC_REQUIRE(P.ok, OC_EINVAL, "wgrad_tc: unsupported shape");
+  OC_REQUIRE(a.n_out <= INT32_MAX, OC_EINVAL, "wgrad_tc: more than 2^31 - 1 rows");
   const size_t partial_bytes = wgrad_tc_partial_bytes(P, a.K, a.Cin, a.Cout);
   const size_t need = partial_bytes + (a.tiled ? 0 : tile_table_bytes(a.n_out, a.K));
   OC_REQUIRE(workspace && workspace_bytes >= need, OC_ENOMEM, "wgrad_tc: workspace %zu < %zu", workspace_bytes, need);

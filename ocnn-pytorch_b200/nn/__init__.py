@@ -1,7 +1,7 @@
 from .octree_pad import octree_pad, octree_depad
 from .octree_conv import (OctreeConv, OctreeDeconv, octree_conv, octree_deconv,
                           OctreeConvFunction, OctreeDeconvFunction, conv_gather, conv_wgrad,
-                          tile_table, tiled_supported, TileTable, tap_mask_order)
+                          tile_table, tiled_supported, TileTable, tap_mask_order, wgrad_by_mask)
 from .octree_dwconv import OctreeDWConv, octree_dwconv
 from .octree_pool import (octree_max_pool, octree_max_unpool, OctreeMaxPool, OctreeMaxUnpool,
                           octree_avg_pool, octree_global_pool, OctreeAvgPool, OctreeGlobalPool)
@@ -14,7 +14,7 @@ from .octree_norm import (OctreeBatchNorm, OctreeGroupNorm, OctreeInstanceNorm, 
                           convert_sync_batchnorm, col_stats)
 
 __all__ = [
-    'octree_pad', 'octree_depad', 'OctreeConv', 'OctreeDeconv', 'octree_conv', 'octree_deconv',
+    'octree_pad', 'octree_depad', 'OctreeConv', 'OctreeDeconv', 'octree_conv', 'octree_deconv', 'wgrad_by_mask',
     'OctreeConvFunction', 'OctreeDeconvFunction', 'conv_gather', 'conv_wgrad', 'tile_table', 'tiled_supported', 'TileTable', 'tap_mask_order', 'OctreeDWConv',
     'octree_dwconv', 'octree_max_pool', 'octree_max_unpool', 'OctreeMaxPool', 'OctreeMaxUnpool',
     'octree_avg_pool', 'octree_global_pool', 'OctreeAvgPool', 'OctreeGlobalPool', 'search_value', 'octree_align',

@@ -190,6 +190,15 @@ class _OctreeDeconv(OctreeConvBase):
   def is_conv_layer(self): return False
 
 
+def wgrad_by_mask(c_in, c_out):
+  r''' Whether the weight-gradient kernel should read the tile table ordered by tap mask
+  (shared with the forward pass) or one in natural row order.  With at most 64 channels on
+  both sides a CTA holds half of the taps or more, and the skipped taps of the mask order pay
+  off; with more channels a CTA holds four taps or fewer, the CTAs of frequent taps then bound
+  the kernel, and the natural order (dense grad_out rows) is faster. '''
+  return max(c_in, c_out) <= 64
+
+
 def _tiles(octree, depth, kernel, stride, nempty, transposed, K, c_in, c_out, data, by_mask=True):
   r''' The octree's cached tile table of this convolution, or None where the
   tensor-core kernel does not apply (then the plain table is used). '''
@@ -228,7 +237,8 @@ class OctreeConvFunction(Function):
       grad_in = conv_gather(grad, weights, True, None, table_t, taps_t, cout, cin, tiles)
     if ctx.needs_input_grad[1] or (has_bias and ctx.needs_input_grad[2]):
       table, taps = octree.conv_table(depth, kernel, stride, nempty)
-      tiles = _tiles(octree, depth, kernel, stride, nempty, False, len(taps), cin, cout, data, by_mask=False)
+      tiles = _tiles(octree, depth, kernel, stride, nempty, False, len(taps), cin, cout, data,
+                     by_mask=wgrad_by_mask(cin, cout))
       gw, gb = conv_wgrad(data, grad, table, taps, cin, cout, has_bias and ctx.needs_input_grad[2], tiles)
       grad_w = gw.to(weights.dtype) if ctx.needs_input_grad[1] else None
       grad_b = gb
@@ -266,7 +276,8 @@ class OctreeDeconvFunction(Function):
       grad_in = conv_gather(grad, weights, False, None, table, taps, cout, cin, tiles)
     if ctx.needs_input_grad[1]:
       # weights are (K, out_channels, in_channels): gathered operand = grad
-      tiles = _tiles(octree, nd, kernel, stride, nempty, False, len(taps), cout, cin, grad, by_mask=False)
+      tiles = _tiles(octree, nd, kernel, stride, nempty, False, len(taps), cout, cin, grad,
+                     by_mask=wgrad_by_mask(cin, cout))
       gw, _ = conv_wgrad(grad, data, table, taps, cout, cin, False, tiles)
       grad_w = gw.to(weights.dtype)
     if has_bias and ctx.needs_input_grad[2]:

@@ -399,8 +399,8 @@ class Octree:
     (:func:`tap_mask_order`): a tile then holds rows with the same few taps and the empty taps
     are skipped - for the inverse table of a stride-2 convolution this groups the rows by child
     index.  The result carries the row order (:class:`TileTable`).  ``by_mask=False`` keeps the
-    natural row order, which the weight-gradient kernel prefers (it pairs taps, so fewer of its
-    stages vanish, and it reads grad_out rows in table order). '''
+    natural row order, which the weight-gradient kernel prefers above 64 channels
+    (``nn.wgrad_by_mask``). '''
     key = ('tiles', depth, kernel, stride, nempty, transposed, by_mask)
     if key not in self._table_cache:
       from ..nn.octree_conv import tile_table, tap_mask_order, TileTable
