@@ -27,6 +27,9 @@
 //                         (H = 1) the producers prefetch and publish the indices themselves.
 // Stages flow through a ring of full/empty mbarriers; the header of a tile's first stage
 // tells the MMA warp how many stages the tile has.  Every wait is bounded.
+#include <cuda.h>
+#include <stdlib.h>
+
 #include "oc_common.cuh"
 #include "conv_internal.cuh"
 #include "tc_ptx.cuh"
@@ -95,6 +98,8 @@ struct Params {
   int NT;              // output channels per CTA tile (multiple of 16, <= 256)
   int stages;
   int tmem_cols;       // power of two >= 2 * H * NT
+  int tma;             // gathered rows come by TMA (tile::gather4 through the kernel's tensor map)
+  int oob_row;         // a row index outside the tensor map: stands for "no neighbour", reads zeros
   TapList taps;
 };
 
@@ -139,7 +144,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, float ba, float bb, 
 // C = 64) and the per-stage bookkeeping of the MMA warp are shared by 256 rows.
 template <bool BF16, typename I, int H>
 __global__ void __launch_bounds__(THREADS, 1)
-conv_tc_kernel(const Params p) {
+conv_tc_kernel(const Params p, const __grid_constant__ CUtensorMap data_map) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: swizzle atoms are 8 rows x 128 B
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -330,6 +335,18 @@ conv_tc_kernel(const Params p) {
 #endif
               }
 #ifndef OC_NOCOPY
+              if (p.tma) {
+                // TMA path (64-channel blocks of whole taps): lane l asks for the rows 4 l .. 4 l + 3
+                // of the block with one tile::gather4 copy; the TMA unit applies the 128-byte
+                // swizzle and completes 512 bytes on the stage's barrier.
+                const int4 r4 = *reinterpret_cast<const int4*>(idx_rows(buf, h) + k_blk * TILE_M + 4 * lane);
+                const int oob = p.oob_row;
+                mbar_arrive_expect_tx(full_bar(s), 512u);
+                tma_gather4(a_dst + (uint32_t)lane * 512u, &data_map, kb_blk * KBLK, r4.x < 0 ? oob : r4.x,
+                            r4.y < 0 ? oob : r4.y, r4.z < 0 ? oob : r4.z, r4.w < 0 ? oob : r4.w, full_bar(s));
+                PROF_T(pw2); PROF_ADD(1, pw2 - pw1); PROF_ADD(2, 1);
+                continue;
+              }
               const int k_lane = k_blk + sub;            // this lane's tap
               const bool live = PACK > 1 ? k_lane < K : chunk * 8 < min(KBLK, Cin - kb_blk * KBLK);
               {
@@ -675,8 +692,44 @@ int prep_weights_tc(const void* w, int w_dtype, int K, int Cin, int Cout, int tr
   return OC_OK;
 }
 
+// Tensor map of a (rows, C) fp16 / bf16 matrix for tile::gather4: box = 64 channels x 1 row,
+// 128-byte swizzle, rows outside the matrix read as zeros.
+static int make_rows_map(const void* base, int64_t rows, int C, int dtype, CUtensorMap* map) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    OC_CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    OC_REQUIRE(fn && q == cudaDriverEntryPointSuccess, OC_ECUDA, "cuTensorMapEncodeTiled is not available");
+    encode = (EncodeFn)fn;
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)C, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)C * 2};
+  const cuuint32_t box[2] = {64, 1};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(map, dtype == OC_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  OC_REQUIRE(r == CUDA_SUCCESS, OC_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return OC_OK;
+}
+
+// Whether the gathered rows come by TMA (tile::gather4) instead of per-lane cp.async: whole
+// 64-channel blocks and 32-bit row numbers, and the environment variable OC_TMA_GATHER=1 (read at
+// every launch).  Both paths give the same bits and, measured on B200, the same speed within 3 %
+// (the gather is bound by the latency of the rows in flight, not by how they are requested), so
+// the cp.async path, which also serves Cin = 16 / 32 and partial blocks, is the default.
+static bool tma_gather_ok(int64_t n_in, int Cin, int pack) {
+  const char* e = getenv("OC_TMA_GATHER");
+  return e && atoi(e) != 0 && pack == 1 && Cin % 64 == 0 && n_in > 0 && n_in < INT32_MAX;
+}
+
 template <bool BF16, typename I, int H>
-static int launch_conv_tc_t(const tc::Params& prm, const tc::Plan& P, cudaStream_t s) {
+static int launch_conv_tc_t(const tc::Params& prm, const tc::Plan& P, const CUtensorMap& map, cudaStream_t s) {
   auto kern = tc::conv_tc_kernel<BF16, I, H>;
   static thread_local int configured_dev = -1;
   int dev = 0;
@@ -688,7 +741,7 @@ static int launch_conv_tc_t(const tc::Params& prm, const tc::Plan& P, cudaStream
   const int64_t n_tiles = cdiv(cdiv(prm.n_out, tc::TILE_M), H);
   const int sms = sm_count();
   dim3 grid((unsigned)(n_tiles < sms ? n_tiles : sms), (unsigned)P.n_tiles_n);
-  kern<<<grid, tc::THREADS, P.smem_bytes, s>>>(prm);
+  kern<<<grid, tc::THREADS, P.smem_bytes, s>>>(prm, map);
   OC_LAUNCH_OK("conv_tc_kernel");
   return OC_OK;
 }
@@ -707,10 +760,18 @@ int launch_conv_tc(const ConvArgs& a, const void* Wimg, int* status_dev, cudaStr
   OC_REQUIRE(((uintptr_t)a.tiled % 16) == 0, OC_EINVAL, "conv_tc: the tile table must be 16-byte aligned");
   prm.n_out = a.n_out; prm.table_cols = a.table_cols; prm.K = a.K; prm.Cin = a.Cin; prm.Cout = a.Cout;
   prm.KB = P.KB; prm.PACK = P.PACK; prm.NBLK = P.NBLK; prm.NT = P.NT; prm.stages = P.stages; prm.tmem_cols = P.tmem_cols; prm.taps = a.taps;
+  alignas(64) CUtensorMap map;
+  memset(&map, 0, sizeof(map));
+  prm.tma = tma_gather_ok(a.n_in, a.Cin, P.PACK) ? 1 : 0;
+  prm.oob_row = (int)a.n_in;
+  if (prm.tma) {
+    int rc = make_rows_map(a.data, a.n_in, a.Cin, a.dtype, &map);
+    if (rc) return rc;
+  }
   const bool bf = a.dtype == OC_BF16;
-  if (P.H == 2) return bf ? launch_conv_tc_t<true, int32_t, 2>(prm, P, s) : launch_conv_tc_t<false, int32_t, 2>(prm, P, s);
-  if (a.idx_bytes == 8) return bf ? launch_conv_tc_t<true, int64_t, 1>(prm, P, s) : launch_conv_tc_t<false, int64_t, 1>(prm, P, s);
-  return bf ? launch_conv_tc_t<true, int32_t, 1>(prm, P, s) : launch_conv_tc_t<false, int32_t, 1>(prm, P, s);
+  if (P.H == 2) return bf ? launch_conv_tc_t<true, int32_t, 2>(prm, P, map, s) : launch_conv_tc_t<false, int32_t, 2>(prm, P, map, s);
+  if (a.idx_bytes == 8) return bf ? launch_conv_tc_t<true, int64_t, 1>(prm, P, map, s) : launch_conv_tc_t<false, int64_t, 1>(prm, P, map, s);
+  return bf ? launch_conv_tc_t<true, int32_t, 1>(prm, P, map, s) : launch_conv_tc_t<false, int32_t, 1>(prm, P, map, s);
 }
 
 int read_tc_status(cudaStream_t s, int* h_status) {

@@ -2,6 +2,8 @@
 the numpy oracle.  Tolerances (relative L2 and max-norm, both must hold):
 fp32 1e-4; fp16 / bf16 1e-2 against an fp32 computation on the same rounded
 inputs.  Integer outputs (pool indices) and pure copies must be equal."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -239,6 +241,16 @@ def test_conv_large_random_table(dtype, cin, cout, n_out):
   y_tiled = b200.nn.conv_gather(x, w, False, bias, table, taps, cin, cout, tiles=tiles)
   b200._lib.status_check(dev())
   assert torch.equal(y_plain, y_tiled)
+  # the same rows fetched by TMA (tile::gather4) instead of cp.async: identical bits
+  # (taken when Cin is a multiple of 64; otherwise the variable changes nothing)
+  os.environ['OC_TMA_GATHER'] = '1'
+  try:
+    y_tma = b200.nn.conv_gather(x, w, False, bias, table, taps, cin, cout, tiles=tiles)
+    y_tma_plain = b200.nn.conv_gather(x, w, False, bias, table, taps, cin, cout)
+    b200._lib.status_check(dev())
+  finally:
+    del os.environ['OC_TMA_GATHER']
+  assert torch.equal(y_plain, y_tma) and torch.equal(y_plain, y_tma_plain)
   # against fp32 torch on a sample of rows (including the empty tile and the ragged end)
   rows = torch.cat([torch.arange(0, 300, device=dev()), torch.arange(4090, 4360, device=dev()),
                     torch.arange(n_out - 200, n_out, device=dev())])
