@@ -234,6 +234,12 @@ int oc_conv_tiled_supported(int K, int Cin, int Cout, int dtype);
 /* masks[r] (int32) = bit k set iff table[r, taps[k]] >= 0: the sort key for row_perm below. */
 int oc_tap_masks(const void* table, int idx_bytes, int table_cols, const int* h_taps, int K,
                  int64_t n_rows, int32_t* masks, void* stream);
+/* perm (device int32 (n_rows)) = the rows of the table sorted, stably, by oc_tap_masks: the
+ * row_perm of oc_tile_table_build below.  An 8-bit LSD radix sort over the K mask bits, the same
+ * kernels that sort the point keys in oc_build_octree_count. */
+size_t oc_tap_order_workspace_bytes(int64_t n_rows);
+int oc_tap_order(const void* table, int idx_bytes, int table_cols, const int* h_taps, int K,
+                 int64_t n_rows, int32_t* perm, void* workspace, size_t workspace_bytes, void* stream);
 size_t oc_tile_table_bytes(int64_t n_out, int K);
 /* n_in > 0: number of feature rows the table indexes; an entry >= n_in is stored as -1 and
  * the next oc_status_check returns OC_EINVAL (the kernels do not re-check indices).  n_in = 0: no check.

@@ -500,6 +500,78 @@ extern "C" int oc_build_octree_emit(const float* points, const float* normals, c
   return OC_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Row order by tap mask: rows of a neighbour table sorted (stably) by the bit mask of
+// their valid taps, with the radix sort of the octree build (mask = key, row = value).
+// ---------------------------------------------------------------------------
+extern "C" int oc_tap_masks(const void* table, int idx_bytes, int table_cols, const int* h_taps, int K,
+                            int64_t n_rows, int32_t* masks, void* stream);
+
+namespace oc {
+struct OrderLayout {
+  size_t key_a, key_b, val_a, val_b, masks, hist, scan_tmp, total;
+  int64_t sort_blocks;
+};
+static OrderLayout order_layout(int64_t n) {
+  OrderLayout L;
+  size_t off = 0;
+  auto take = [&](size_t b) { size_t o = off; off += align_up(b, 256); return o; };
+  const int64_t m = n > 0 ? n : 1;
+  L.sort_blocks = cdiv(m, SORT_TILE);
+  L.key_a = take((size_t)m * 8);
+  L.key_b = take((size_t)m * 8);
+  L.val_a = take((size_t)m * 4);
+  L.val_b = take((size_t)m * 4);
+  L.masks = take((size_t)m * 4);
+  L.hist = take((size_t)RADIX * L.sort_blocks * 4);
+  L.scan_tmp = take(scan_workspace_bytes((int64_t)RADIX * L.sort_blocks));
+  L.total = off;
+  return L;
+}
+__global__ void mask_key_kernel(const int32_t* __restrict__ masks, int64_t n, uint64_t* __restrict__ key,
+                                uint32_t* __restrict__ val) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    key[i] = (uint64_t)(uint32_t)masks[i];
+    val[i] = (uint32_t)i;
+  }
+}
+}  // namespace oc
+
+extern "C" size_t oc_tap_order_workspace_bytes(int64_t n_rows) { return oc::order_layout(n_rows).total; }
+
+extern "C" int oc_tap_order(const void* table, int idx_bytes, int table_cols, const int* h_taps, int K,
+                            int64_t n_rows, int32_t* perm, void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace oc;
+  cudaStream_t s = (cudaStream_t)stream;
+  OC_REQUIRE(n_rows >= 0 && n_rows < INT32_MAX, OC_EINVAL, "tap_order: n_rows %lld", (long long)n_rows);
+  if (n_rows == 0) return OC_OK;
+  const OrderLayout L = order_layout(n_rows);
+  OC_REQUIRE(perm && workspace && workspace_bytes >= L.total, OC_ENOMEM, "tap_order: workspace %zu < %zu",
+             workspace_bytes, L.total);
+  uint8_t* ws = (uint8_t*)workspace;
+  uint64_t *kin = (uint64_t*)(ws + L.key_a), *kout = (uint64_t*)(ws + L.key_b);
+  uint32_t *vin = (uint32_t*)(ws + L.val_a), *vout = (uint32_t*)(ws + L.val_b);
+  int32_t* masks = (int32_t*)(ws + L.masks);
+  uint32_t* hist = (uint32_t*)(ws + L.hist);
+  int32_t* scan_tmp = (int32_t*)(ws + L.scan_tmp);
+  int rc = oc_tap_masks(table, idx_bytes, table_cols, h_taps, K, n_rows, masks, stream);
+  if (rc) return rc;
+  mask_key_kernel<<<grid1d(n_rows), 256, 0, s>>>(masks, n_rows, kin, vin);
+  OC_LAUNCH_OK("mask_key_kernel");
+  const int64_t nb = L.sort_blocks;
+  for (int shift = 0; shift < K; shift += RADIX_BITS) {
+    radix_hist_kernel<<<(unsigned)nb, SORT_THREADS, 0, s>>>(kin, n_rows, shift, hist, nb);
+    OC_CUDA_OK(device_scan(HistFlag{hist}, HistSink{hist}, (int64_t)RADIX * nb, nullptr, scan_tmp, nullptr, s));
+    radix_scatter_kernel<<<(unsigned)nb, SORT_THREADS, 0, s>>>(kin, vin, n_rows, shift, hist, nb, kout, vout);
+    OC_LAUNCH_OK("radix_scatter_kernel");
+    uint64_t* tk = kin; kin = kout; kout = tk;
+    uint32_t* tv = vin; vin = vout; vout = tv;
+  }
+  OC_CUDA_OK(cudaMemcpyAsync(perm, vin, (size_t)n_rows * 4, cudaMemcpyDeviceToDevice, s));
+  return OC_OK;
+}
+
 extern "C" int oc_full_layer(int depth, int batch_size, int64_t* keys, int32_t* children, void* stream) {
   OC_REQUIRE(depth >= 0 && depth <= 10 && batch_size >= 1, OC_EINVAL, "oc_full_layer: bad depth/batch");
   const int64_t n = (int64_t)batch_size << (3 * depth);

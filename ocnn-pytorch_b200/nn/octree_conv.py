@@ -42,10 +42,11 @@ def tap_mask_order(table, taps):
   and the kernels skip the taps that are empty in a whole tile. '''
   _lib.require_cuda(table)
   n = table.shape[0]
-  masks = torch.empty(n, dtype=torch.int32, device=table.device)
-  _lib.call('oc_tap_masks', _lib.ptr(table), _idx_bytes(table), table.shape[1], _lib.int_array(taps), len(taps), n,
-            _lib.ptr(masks), _lib.stream(table.device))
-  return torch.sort(masks, stable=True)[1].to(torch.int32).contiguous()
+  perm = torch.empty(n, dtype=torch.int32, device=table.device)
+  ws = _lib.workspace(_lib.lib().oc_tap_order_workspace_bytes(n), table.device)
+  _lib.call('oc_tap_order', _lib.ptr(table), _idx_bytes(table), table.shape[1], _lib.int_array(taps), len(taps), n,
+            _lib.ptr(perm), _lib.ptr(ws), ws.numel(), _lib.stream(table.device))
+  return perm
 
 
 def tile_table(table, taps, n_in=0, perm=None):

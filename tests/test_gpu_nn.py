@@ -169,6 +169,7 @@ def test_tile_table_layout_and_equivalence(mid_octree):
     assert np.array_equal(np.sort(order), np.arange(n_out))
     row_mask = ((to_np(table)[:, taps] >= 0) * (1 << np.arange(K))[None, :]).sum(axis=1)
     assert (np.diff(row_mask[order]) >= 0).all()                 # mask never decreases along the table
+    assert np.array_equal(order, np.argsort(row_mask, kind='stable'))   # ties keep the table's order
     if transposed and stride == 2:
       cidx = to_np(octree.key(d, nempty) & 7)[order]              # which groups the rows by child index
       assert len(np.unique(cidx[:-1] != cidx[1:], return_counts=True)[1]) <= 2 and (cidx[:-1] != cidx[1:]).sum() < 64
