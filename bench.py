@@ -420,17 +420,23 @@ def run_conv_only(args, b200, octree, dev):
   print(json.dumps(out))
 
 
+LAST_DEVICE_ALLOCS = 0   # cudaMalloc calls of torch's allocator inside the last timed region of _time
+
+
 def _time(fn, reps=10, warm=3):
   import torch
+  global LAST_DEVICE_ALLOCS
   for _ in range(warm):
     fn()
   torch.cuda.synchronize()
+  a0 = torch.cuda.memory_stats().get('num_device_alloc', 0)
   e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
   e0.record()
   for _ in range(reps):
     fn()
   e1.record()
   torch.cuda.synchronize()
+  LAST_DEVICE_ALLOCS = torch.cuda.memory_stats().get('num_device_alloc', 0) - a0
   return e0.elapsed_time(e1) / reps
 
 
@@ -451,6 +457,10 @@ def run_suite(args, b200, octree, dev):
       o['gbs'] = round(nbytes / ms / 1e6, 1)
       o['frac_hbm_peak'] = round(nbytes / ms / 1e6 / pk['hbm'], 4)
     o.update(kw)
+    allocs = kw.pop('allocs', LAST_DEVICE_ALLOCS)
+    o.pop('allocs', None)
+    if allocs:      # the timed region paid for cudaMalloc calls of torch's caching allocator
+      o['device_allocs_in_timed_region'] = allocs
     print(json.dumps(o), flush=True)
 
   for nempty in (False, True):
@@ -552,8 +562,12 @@ def run_suite(args, b200, octree, dev):
 
   def neigh_only():
     holder['o'].construct_all_neigh()
-  t_b = _time(build_only, 3, 1)
-  t_n = _time(neigh_only, 3, 1)
+  # three warm-up rounds: both generations of tables (the new one is built while the old one is
+  # still referenced) then sit in torch's caching allocator, and no cudaMalloc is timed
+  t_b = _time(build_only, 5, 3)
+  allocs_b = LAST_DEVICE_ALLOCS
+  t_n = _time(neigh_only, 5, 3)
+  allocs_n = LAST_DEVICE_ALLOCS
   o = holder['o']
   P = nb * npts
   nn_ = [int(v) for v in o.nnum]
@@ -561,9 +575,9 @@ def run_suite(args, b200, octree, dev):
   build_bytes = P * (12 + 12 + 12) + P * 12 * 2 * passes + sum(nn_) * 12 + int(o.nnum_nempty[depth]) * 36
   # written: every table; read: the rows of the non-empty parents (nnum[d] / 8 of them) + all child pointers
   neigh_bytes = sum(nn_[1:]) * 27 * 8 + sum(nn_[1:]) // 8 * 27 * (8 + 4) + sum(nn_[:-1]) * 4
-  emit('build_octree depth10 (16 x 200k pts, device resident)', t_b, nbytes=build_bytes, mpts_per_s=round(P / t_b / 1e3, 1), nnum=nn_)
-  emit('construct_all_neigh depth10', t_n, nbytes=neigh_bytes, mpts_per_s=round(P / t_n / 1e3, 1))
-  emit('build + neigh depth10', t_b + t_n, nbytes=build_bytes + neigh_bytes, mpts_per_s=round(P / (t_b + t_n) / 1e3, 1))
+  emit('build_octree depth10 (16 x 200k pts, device resident)', t_b, nbytes=build_bytes, mpts_per_s=round(P / t_b / 1e3, 1), nnum=nn_, allocs=allocs_b)
+  emit('construct_all_neigh depth10', t_n, nbytes=neigh_bytes, mpts_per_s=round(P / t_n / 1e3, 1), allocs=allocs_n)
+  emit('build + neigh depth10', t_b + t_n, nbytes=build_bytes + neigh_bytes, mpts_per_s=round(P / (t_b + t_n) / 1e3, 1), allocs=allocs_b + allocs_n)
   b200._lib.status_check(dev)
 
 

@@ -530,9 +530,8 @@ static OrderLayout order_layout(int64_t n) {
 }
 __global__ void mask_key_kernel(const int32_t* __restrict__ masks, int64_t n, uint64_t* __restrict__ key,
                                 uint32_t* __restrict__ val) {
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) {
-    key[i] = (uint64_t)(uint32_t)masks[i];
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    key[i] = (uint64_t)(uint32_t)masks[i];     // grid1d caps the grid: a grid-stride loop
     val[i] = (uint32_t)i;
   }
 }

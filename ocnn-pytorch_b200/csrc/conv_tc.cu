@@ -493,7 +493,10 @@ conv_tc_kernel(const Params p, const __grid_constant__ CUtensorMap data_map) {
 #pragma unroll
       for (int h = 0; h < H; ++h) {
         int64_t row = (tile * H + h) * TILE_M + warp * 32 + lane;     // position in the tile table
-        if (p.perm && row < p.n_out) row = p.perm[row];               // -> output row
+        if (p.perm && row < p.n_out) {                                // -> output row
+          row = p.perm[row];
+          if (row < 0) row = p.n_out;                                 // not a row number: nothing is written
+        }
         const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (acc * H + h) * (uint32_t)p.NT;
         for (int c0 = 0; c0 < p.NT; c0 += 16) {
           uint32_t r[16];
@@ -634,12 +637,16 @@ tile_table_kernel(const I* __restrict__ table, int table_cols, TapList taps, int
   __syncthreads();
   const int64_t tile = blockIdx.x;
   const int64_t pos = tile * tc::TILE_M + threadIdx.x;        // position in the tile table
-  const int64_t r = (perm && pos < n_out) ? (int64_t)perm[pos] : pos;   // row of the plain table
+  int64_t r = (perm && pos < n_out) ? (int64_t)perm[pos] : pos;   // row of the plain table
+  if (r < 0 || (pos < n_out && r >= n_out)) {                     // not a permutation of the rows: reported
+    atomicMax(&g_tc_status, 90);
+    r = n_out;
+  }
   uint8_t* blk = out + (size_t)tile * block_bytes;
   int* rows = (int*)(blk + tc::IDX_HDR_BYTES);
   uint32_t m = 0;
   for (int k = 0; k < K; ++k) {
-    int64_t v64 = pos < n_out ? (int64_t)table[r * table_cols + taps.t[k]] : -1;
+    int64_t v64 = (pos < n_out && r < n_out) ? (int64_t)table[r * table_cols + taps.t[k]] : -1;
     if (n_in > 0 && v64 >= n_in) {   // would read past the feature rows: dropped and reported
       v64 = -1;
       atomicMax(&g_tc_status, 90);

@@ -308,6 +308,7 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
       const int64_t pos = tile * TILE_R + gq * 32 + lane;
       int my_row = -1;
       if (pos < p.n_out) my_row = p.perm ? p.perm[pos] : (int)pos;
+      if (my_row >= p.n_out) my_row = -1;                   // not a row number: zeros
       if (!mbar_wait(gempty_bar(b), ((it >> 1) & 1u) ^ 1u, abort_flag, &g_tc_status, 11)) break;
       const uint32_t g_dst = s_base + L.gbuf + b * (uint32_t)(p.GB * BLK_BYTES) + (uint32_t)gq * 32u * 128u;
       for (int gb = 0; gb < p.GB; ++gb) {

@@ -459,3 +459,31 @@ def test_conv_error_paths(syn_octree):
     b200.nn.OctreeConv(4, 8, [4]).to(dev())(torch.zeros(int(syn_octree.nnum[5]), 4, device=dev()), syn_octree, 5)
   with pytest.raises(TypeError):
     m.double()(torch.zeros(int(syn_octree.nnum[5]), 4, device=dev(), dtype=torch.float64), syn_octree, 5)
+
+
+def test_tap_order_large_and_bad_row_order():
+  # More rows than one wave of the helper kernels covers (grids are capped, kernels stride):
+  # the order is the stable sort of the rows by their mask of valid taps.
+  g = torch.Generator(device=dev()).manual_seed(5)
+  n, K = 148 * 16 * 256 + 12345, 27
+  table = torch.randint(0, 1000, (n, K), device=dev(), generator=g)
+  table[torch.rand(n, K, device=dev(), generator=g) < 0.5] = -1
+  table[: n // 3, 9:] = -1                        # many rows share few masks
+  taps = list(range(K))
+  order = to_np(b200.nn.tap_mask_order(table, taps)).astype(np.int64)
+  masks = ((to_np(table) >= 0) * (1 << np.arange(K))[None, :]).sum(axis=1)
+  assert np.array_equal(order, np.argsort(masks, kind='stable'))
+  # fewer taps than a sort pass, and a single row
+  order5 = to_np(b200.nn.tap_mask_order(table[:5000], [3, 0, 7])).astype(np.int64)
+  m5 = ((to_np(table[:5000])[:, [3, 0, 7]] >= 0) * np.array([1, 2, 4])[None, :]).sum(axis=1)
+  assert np.array_equal(order5, np.argsort(m5, kind='stable'))
+  assert to_np(b200.nn.tap_mask_order(table[:1], taps)).tolist() == [0]
+  # a row order that is not a permutation of the rows is reported when the tile table is built
+  small = table[:1000].contiguous()
+  bad = torch.arange(1000, device=dev(), dtype=torch.int32)
+  bad[17] = 5000
+  b200._lib.status_check(dev())
+  b200.nn.tile_table(small, taps, 0, bad)
+  with pytest.raises(b200._lib.OctConvError):
+    b200._lib.status_check(dev())
+  b200._lib.status_check(dev())
