@@ -41,8 +41,9 @@ def workload_clouds(rank=0, batch=None, npts=NPTS):
 
 
 # dram__bytes_read + dram__bytes_write of one forward launch, per output row, from the ncu capture of
-# the 4-octree case (332.8 MB / 1 001 304 rows; traffic grows in proportion to the rows)
-DRAM_BYTES_PER_ROW = 332.4
+# the 4-octree case (537.6 MB read + 112.8 MB written / 1 001 304 rows, tile table ordered by tap
+# mask; traffic grows in proportion to the rows)
+DRAM_BYTES_PER_ROW = 649.5
 
 
 def peaks():
