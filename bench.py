@@ -479,7 +479,7 @@ def run_suite(args, b200, octree, dev):
         fl = 2.0 * nnz * C * C
         tag = dict(C=C, dtype=str(dtype).split('.')[-1], nempty=nempty, rows=n, valid_taps=nnz)
         tl, tl_t = octree.conv_tiles(D, '333', 1, nempty), octree.conv_tiles(D, '333', 1, nempty, True)
-        tl_w = octree.conv_tiles(D, '333', 1, nempty, False, by_mask=b200.nn.wgrad_by_mask(C, C))
+        tl_w = octree.conv_tiles(D, '333', 1, nempty, False, by_mask=b200.nn.wgrad_by_mask(C, C, nempty))
         emit('conv333_fwd', _time(lambda: b200.nn.conv_gather(x, w, False, None, table, taps, C, C, tl)), flops=fl, **tag)
         emit('conv333_dgrad', _time(lambda: b200.nn.conv_gather(gy, w, True, None, table_t, taps_t, C, C, tl_t)), flops=fl, **tag)
         emit('conv333_wgrad', _time(lambda: b200.nn.conv_wgrad(x, gy, table, taps, C, C, False, tl_w)), flops=fl, **tag)

@@ -191,13 +191,15 @@ class _OctreeDeconv(OctreeConvBase):
   def is_conv_layer(self): return False
 
 
-def wgrad_by_mask(c_in, c_out):
+def wgrad_by_mask(c_in, c_out, nempty=False):
   r''' Whether the weight-gradient kernel should read the tile table ordered by tap mask
   (shared with the forward pass) or one in natural row order.  With at most 64 channels on
   both sides a CTA holds half of the taps or more, and the skipped taps of the mask order pay
   off; with more channels a CTA holds four taps or fewer, the CTAs of frequent taps then bound
-  the kernel, and the natural order (dense grad_out rows) is faster. '''
-  return max(c_in, c_out) <= 64
+  the kernel, and the natural order (dense grad_out rows) is faster - unless the table is over
+  the non-empty nodes only, where so few taps are valid (a quarter of the slots on a surface
+  octree) that the mask order wins at every width. '''
+  return nempty or max(c_in, c_out) <= 64
 
 
 def _tiles(octree, depth, kernel, stride, nempty, transposed, K, c_in, c_out, data, by_mask=True):
@@ -239,7 +241,7 @@ class OctreeConvFunction(Function):
     if ctx.needs_input_grad[1] or (has_bias and ctx.needs_input_grad[2]):
       table, taps = octree.conv_table(depth, kernel, stride, nempty)
       tiles = _tiles(octree, depth, kernel, stride, nempty, False, len(taps), cin, cout, data,
-                     by_mask=wgrad_by_mask(cin, cout))
+                     by_mask=wgrad_by_mask(cin, cout, nempty))
       gw, gb = conv_wgrad(data, grad, table, taps, cin, cout, has_bias and ctx.needs_input_grad[2], tiles)
       grad_w = gw.to(weights.dtype) if ctx.needs_input_grad[1] else None
       grad_b = gb
@@ -278,7 +280,7 @@ class OctreeDeconvFunction(Function):
     if ctx.needs_input_grad[1]:
       # weights are (K, out_channels, in_channels): gathered operand = grad
       tiles = _tiles(octree, nd, kernel, stride, nempty, False, len(taps), cout, cin, grad,
-                     by_mask=wgrad_by_mask(cin, cout))
+                     by_mask=wgrad_by_mask(cin, cout, nempty))
       gw, _ = conv_wgrad(grad, data, table, taps, cout, cin, False, tiles)
       grad_w = gw.to(weights.dtype)
     if has_bias and ctx.needs_input_grad[2]:
