@@ -236,10 +236,13 @@ int oc_tap_masks(const void* table, int idx_bytes, int table_cols, const int* h_
                  int64_t n_rows, int32_t* masks, void* stream);
 /* perm (device int32 (n_rows)) = the rows of the table sorted, stably, by oc_tap_masks: the
  * row_perm of oc_tile_table_build below.  An 8-bit LSD radix sort over the K mask bits, the same
- * kernels that sort the point keys in oc_build_octree_count. */
+ * kernels that sort the point keys in oc_build_octree_count.  chunk_log2 > 0: the rows are sorted
+ * within consecutive chunks of 2^chunk_log2 rows only (key = chunk number, then mask), which keeps
+ * the rows of a tile within one neighbourhood of the octree; 0: one sort over all rows. */
 size_t oc_tap_order_workspace_bytes(int64_t n_rows);
 int oc_tap_order(const void* table, int idx_bytes, int table_cols, const int* h_taps, int K,
-                 int64_t n_rows, int32_t* perm, void* workspace, size_t workspace_bytes, void* stream);
+                 int64_t n_rows, int chunk_log2, int32_t* perm, void* workspace, size_t workspace_bytes,
+                 void* stream);
 size_t oc_tile_table_bytes(int64_t n_out, int K);
 /* n_in > 0: number of feature rows the table indexes; an entry >= n_in is stored as -1 and
  * the next oc_status_check returns OC_EINVAL (the kernels do not re-check indices).  n_in = 0: no check.

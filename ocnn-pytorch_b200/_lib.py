@@ -58,7 +58,7 @@ PROTOTYPES = {
     'oc_conv_tiled_supported': (_i, [_i, _i, _i, _i]),
     'oc_tap_masks': (_i, [_vp, _i, _i, _ip, _i, _i64, _vp, _vp]),
     'oc_tap_order_workspace_bytes': (_sz, [_i64]),
-    'oc_tap_order': (_i, [_vp, _i, _i, _ip, _i, _i64, _vp, _vp, _sz, _vp]),
+    'oc_tap_order': (_i, [_vp, _i, _i, _ip, _i, _i64, _i, _vp, _vp, _sz, _vp]),
     'oc_tile_table_bytes': (_sz, [_i64, _i]),
     'oc_tile_table_build': (_i, [_vp, _i, _i, _ip, _i, _i64, _i64, _vp, _vp, _sz, _vp]),
     'oc_conv_fwd_tiled': (_i, [_vp, _i64, _vp, _i, _i, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _vp, _vp, _sz, _vp]),

@@ -528,10 +528,11 @@ static OrderLayout order_layout(int64_t n) {
   L.total = off;
   return L;
 }
-__global__ void mask_key_kernel(const int32_t* __restrict__ masks, int64_t n, uint64_t* __restrict__ key,
-                                uint32_t* __restrict__ val) {
+__global__ void mask_key_kernel(const int32_t* __restrict__ masks, int64_t n, int K, int chunk_shift,
+                                uint64_t* __restrict__ key, uint32_t* __restrict__ val) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    key[i] = (uint64_t)(uint32_t)masks[i];     // grid1d caps the grid: a grid-stride loop
+    // grid1d caps the grid: a grid-stride loop.  Key = (chunk of the row, mask).
+    key[i] = ((uint64_t)(i >> chunk_shift) << K) | (uint64_t)(uint32_t)masks[i];
     val[i] = (uint32_t)i;
   }
 }
@@ -540,7 +541,8 @@ __global__ void mask_key_kernel(const int32_t* __restrict__ masks, int64_t n, ui
 extern "C" size_t oc_tap_order_workspace_bytes(int64_t n_rows) { return oc::order_layout(n_rows).total; }
 
 extern "C" int oc_tap_order(const void* table, int idx_bytes, int table_cols, const int* h_taps, int K,
-                            int64_t n_rows, int32_t* perm, void* workspace, size_t workspace_bytes, void* stream) {
+                            int64_t n_rows, int chunk_log2, int32_t* perm, void* workspace, size_t workspace_bytes,
+                            void* stream) {
   using namespace oc;
   cudaStream_t s = (cudaStream_t)stream;
   OC_REQUIRE(n_rows >= 0 && n_rows < INT32_MAX, OC_EINVAL, "tap_order: n_rows %lld", (long long)n_rows);
@@ -556,10 +558,14 @@ extern "C" int oc_tap_order(const void* table, int idx_bytes, int table_cols, co
   int32_t* scan_tmp = (int32_t*)(ws + L.scan_tmp);
   int rc = oc_tap_masks(table, idx_bytes, table_cols, h_taps, K, n_rows, masks, stream);
   if (rc) return rc;
-  mask_key_kernel<<<grid1d(n_rows), 256, 0, s>>>(masks, n_rows, kin, vin);
+  OC_REQUIRE(chunk_log2 >= 0 && chunk_log2 < 32, OC_EINVAL, "tap_order: chunk_log2 %d", chunk_log2);
+  const int chunk_shift = chunk_log2 > 0 ? chunk_log2 : 31;         // 0: one chunk (n_rows < 2^31)
+  int key_bits = K;
+  while (((n_rows - 1) >> chunk_shift) >> (key_bits - K)) ++key_bits;   // + bits of the last chunk's number
+  mask_key_kernel<<<grid1d(n_rows), 256, 0, s>>>(masks, n_rows, K, chunk_shift, kin, vin);
   OC_LAUNCH_OK("mask_key_kernel");
   const int64_t nb = L.sort_blocks;
-  for (int shift = 0; shift < K; shift += RADIX_BITS) {
+  for (int shift = 0; shift < key_bits; shift += RADIX_BITS) {
     radix_hist_kernel<<<(unsigned)nb, SORT_THREADS, 0, s>>>(kin, n_rows, shift, hist, nb);
     OC_CUDA_OK(device_scan(HistFlag{hist}, HistSink{hist}, (int64_t)RADIX * nb, nullptr, scan_tmp, nullptr, s));
     radix_scatter_kernel<<<(unsigned)nb, SORT_THREADS, 0, s>>>(kin, vin, n_rows, shift, hist, nb, kout, vout);

@@ -36,16 +36,23 @@ class TileTable:
     self.perm = perm
 
 
-def tap_mask_order(table, taps):
+ORDER_CHUNK_LOG2 = 19   # rows are ordered by tap mask within chunks of 2^19 consecutive rows
+
+
+def tap_mask_order(table, taps, chunk_log2=ORDER_CHUNK_LOG2):
   r''' Rows of `table` sorted (stably) by the bit mask of their valid taps, as an int32
   permutation.  Tiles of a tile table built in this order hold rows with the same few taps,
-  and the kernels skip the taps that are empty in a whole tile. '''
+  and the kernels skip the taps that are empty in a whole tile.  The sort runs within chunks
+  of ``2**chunk_log2`` consecutive rows (0: over all rows at once): rows are in z-order, so
+  a chunk is a neighbourhood of the octree and the rows a tile gathers stay close in memory
+  however many octrees the batch holds; half a million rows per chunk lose 3 % of the skipped
+  taps of the global order and run 2 % faster on the 4 M-row benchmark level. '''
   _lib.require_cuda(table)
   n = table.shape[0]
   perm = torch.empty(n, dtype=torch.int32, device=table.device)
   ws = _lib.workspace(_lib.lib().oc_tap_order_workspace_bytes(n), table.device)
   _lib.call('oc_tap_order', _lib.ptr(table), _idx_bytes(table), table.shape[1], _lib.int_array(taps), len(taps), n,
-            _lib.ptr(perm), _lib.ptr(ws), ws.numel(), _lib.stream(table.device))
+            int(chunk_log2), _lib.ptr(perm), _lib.ptr(ws), ws.numel(), _lib.stream(table.device))
   return perm
 
 

@@ -470,13 +470,18 @@ def test_tap_order_large_and_bad_row_order():
   table[torch.rand(n, K, device=dev(), generator=g) < 0.5] = -1
   table[: n // 3, 9:] = -1                        # many rows share few masks
   taps = list(range(K))
-  order = to_np(b200.nn.tap_mask_order(table, taps)).astype(np.int64)
+  order = to_np(b200.nn.tap_mask_order(table, taps, 0)).astype(np.int64)
   masks = ((to_np(table) >= 0) * (1 << np.arange(K))[None, :]).sum(axis=1)
   assert np.array_equal(order, np.argsort(masks, kind='stable'))
+  # within chunks of 2^17 rows (the default is 2^19: two chunks here)
+  for lg in (17, 19):
+    order_c = to_np(b200.nn.tap_mask_order(table, taps, lg)).astype(np.int64)
+    key = ((np.arange(n) >> lg) << K) | masks
+    assert np.array_equal(order_c, np.argsort(key, kind='stable'))
   # fewer taps than a sort pass, and a single row
-  order5 = to_np(b200.nn.tap_mask_order(table[:5000], [3, 0, 7])).astype(np.int64)
+  order5 = to_np(b200.nn.tap_mask_order(table[:5000], [3, 0, 7], 10)).astype(np.int64)
   m5 = ((to_np(table[:5000])[:, [3, 0, 7]] >= 0) * np.array([1, 2, 4])[None, :]).sum(axis=1)
-  assert np.array_equal(order5, np.argsort(m5, kind='stable'))
+  assert np.array_equal(order5, np.argsort(((np.arange(5000) >> 10) << 3) | m5, kind='stable'))
   assert to_np(b200.nn.tap_mask_order(table[:1], taps)).tolist() == [0]
   # a row order that is not a permutation of the rows is reported when the tile table is built
   small = table[:1000].contiguous()
