@@ -200,13 +200,13 @@ class _OctreeDeconv(OctreeConvBase):
 
 def wgrad_by_mask(c_in, c_out, nempty=False):
   r''' Whether the weight-gradient kernel should read the tile table ordered by tap mask
-  (shared with the forward pass) or one in natural row order.  With at most 64 channels on
-  both sides a CTA holds half of the taps or more, and the skipped taps of the mask order pay
-  off; with more channels a CTA holds four taps or fewer, the CTAs of frequent taps then bound
-  the kernel, and the natural order (dense grad_out rows) is faster - unless the table is over
-  the non-empty nodes only, where so few taps are valid (a quarter of the slots on a surface
-  octree) that the mask order wins at every width. '''
-  return nempty or max(c_in, c_out) <= 64
+  (shared with the forward pass) or one in natural row order.  The mask order skips taps but
+  scatters the grad_out rows, and with many channels a CTA holds few taps, so that the CTAs
+  of the frequent taps bound the launch.  Measured on the depth-8 benchmark level: the mask
+  order wins up to 128 channels (C=64 1.57 -> 1.42 ms, C=128 3.60 -> 3.56 ms) and on tables
+  over the non-empty nodes at every width (a quarter of their slots are valid; C=256
+  3.69 -> 3.21 ms); at 256 channels on a full table the natural order is 6 % faster. '''
+  return nempty or max(c_in, c_out) <= 128
 
 
 def _tiles(octree, depth, kernel, stride, nempty, transposed, K, c_in, c_out, data, by_mask=True):
