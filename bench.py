@@ -544,9 +544,11 @@ def run_suite(args, b200, octree, dev):
   emit('octree_linear_pts C=96 fp16', _time(lambda: b200.nn.octree_linear_pts(xi, octree, D, q)),
        nbytes=M * (16 + 8 * 12) + M * Ci * s, rows=M)
   del x, xc, xne, xi, q
-  # octree construction: config 4 shape (200k points per cloud, depth 10), bounded to 16 clouds
+  # octree construction: 64 clouds of 200k points, depth 10 (about 50 GB of neighbour tables)
   import ocnn_pytorch_b200 as B
-  nb, npts, depth = 16, 200000, 10
+  octree._invalidate()
+  torch.cuda.empty_cache()
+  nb, npts, depth = args.build_clouds, 200000, 10
   clouds = [B.synthetic.mixed_cloud(4000 + i, npts, jitter=0.005) for i in range(nb)]
   pts = torch.from_numpy(np.concatenate([c[0] for c in clouds])).to(dev)
   nrm = torch.from_numpy(np.concatenate([c[1] for c in clouds])).to(dev)
@@ -562,6 +564,7 @@ def run_suite(args, b200, octree, dev):
     holder['o'] = o
 
   def neigh_only():
+    holder['o'].neighs = [None] * (depth + 1)      # one generation of tables at a time
     holder['o'].construct_all_neigh()
   # three warm-up rounds: both generations of tables (the new one is built while the old one is
   # still referenced) then sit in torch's caching allocator, and no cudaMalloc is timed
@@ -576,7 +579,7 @@ def run_suite(args, b200, octree, dev):
   build_bytes = P * (12 + 12 + 12) + P * 12 * 2 * passes + sum(nn_) * 12 + int(o.nnum_nempty[depth]) * 36
   # written: every table; read: the rows of the non-empty parents (nnum[d] / 8 of them) + all child pointers
   neigh_bytes = sum(nn_[1:]) * 27 * 8 + sum(nn_[1:]) // 8 * 27 * (8 + 4) + sum(nn_[:-1]) * 4
-  emit('build_octree depth10 (16 x 200k pts, device resident)', t_b, nbytes=build_bytes, mpts_per_s=round(P / t_b / 1e3, 1), nnum=nn_, allocs=allocs_b)
+  emit('build_octree depth10 (%d x 200k pts, device resident)' % nb, t_b, nbytes=build_bytes, mpts_per_s=round(P / t_b / 1e3, 1), nnum=nn_, allocs=allocs_b)
   emit('construct_all_neigh depth10', t_n, nbytes=neigh_bytes, mpts_per_s=round(P / t_n / 1e3, 1), allocs=allocs_n)
   emit('build + neigh depth10', t_b + t_n, nbytes=build_bytes + neigh_bytes, mpts_per_s=round(P / (t_b + t_n) / 1e3, 1), allocs=allocs_b + allocs_n)
   b200._lib.status_check(dev)
@@ -592,6 +595,8 @@ def main():
   ap.add_argument('--batch', type=int, default=BATCH,
                   help='octrees per rank (default 16 = the benchmark configuration; smaller values '
                        'are for profiler captures)')
+  ap.add_argument('--build-clouds', type=int, default=64,
+                  help="point clouds of 200k points in the suite's octree-construction lines")
   ap.add_argument('--mode', default='full', choices=['full', 'conv', 'suite'],
                   help="'conv' runs only the timed conv steps (no build timing, e2e or CPU baseline)")
   args = ap.parse_args()
