@@ -203,6 +203,8 @@ def run_ours(args):
     return run_conv_only(args, b200, octree, dev)
   if args.mode == 'suite':
     return run_suite(args, b200, octree, dev)
+  if args.mode == 'build':
+    return run_build_lines(args, octree, dev, _make_emit(peaks()), torch.Generator(device=dev).manual_seed(0))
   # octree build throughput (secondary figure): host points -> octree + all neighbour tables
   t_build = []
   for i in range(3):
@@ -441,14 +443,7 @@ def _time(fn, reps=10, warm=3):
   return e0.elapsed_time(e1) / reps
 
 
-def run_suite(args, b200, octree, dev):
-  """Secondary measurements: every kernel family of the path on the benchmark batch, one JSON
-  line each (ms, achieved TFLOP/s or GB/s from algorithmic work, fraction of the measured peak)."""
-  import torch
-  pk = peaks()
-  g = torch.Generator(device=dev).manual_seed(0)
-  D = DEPTH
-
+def _make_emit(pk):
   def emit(name, ms, flops=None, nbytes=None, **kw):
     o = {'op': name, 'ms': round(ms, 4)}
     if flops is not None:
@@ -463,6 +458,18 @@ def run_suite(args, b200, octree, dev):
     if allocs:      # the timed region paid for cudaMalloc calls of torch's caching allocator
       o['device_allocs_in_timed_region'] = allocs
     print(json.dumps(o), flush=True)
+  return emit
+
+
+def run_suite(args, b200, octree, dev):
+  """Secondary measurements: every kernel family of the path on the benchmark batch, one JSON
+  line each (ms, achieved TFLOP/s or GB/s from algorithmic work, fraction of the measured peak)."""
+  import torch
+  pk = peaks()
+  g = torch.Generator(device=dev).manual_seed(0)
+  D = DEPTH
+
+  emit = _make_emit(pk)
 
   for nempty in (False, True):
     n = int(octree.nnum_nempty[D] if nempty else octree.nnum[D])
@@ -544,6 +551,12 @@ def run_suite(args, b200, octree, dev):
   emit('octree_linear_pts C=96 fp16', _time(lambda: b200.nn.octree_linear_pts(xi, octree, D, q)),
        nbytes=M * (16 + 8 * 12) + M * Ci * s, rows=M)
   del x, xc, xne, xi, q
+  run_build_lines(args, octree, dev, emit, g)
+
+
+def run_build_lines(args, octree, dev, emit, g):
+  """Octree construction lines: build_octree and construct_all_neigh on clouds of 200k points."""
+  import torch
   # octree construction: 64 clouds of 200k points, depth 10 (about 50 GB of neighbour tables)
   import ocnn_pytorch_b200 as B
   octree._invalidate()
@@ -582,7 +595,7 @@ def run_suite(args, b200, octree, dev):
   emit('build_octree depth10 (%d x 200k pts, device resident)' % nb, t_b, nbytes=build_bytes, mpts_per_s=round(P / t_b / 1e3, 1), nnum=nn_, allocs=allocs_b)
   emit('construct_all_neigh depth10', t_n, nbytes=neigh_bytes, mpts_per_s=round(P / t_n / 1e3, 1), allocs=allocs_n)
   emit('build + neigh depth10', t_b + t_n, nbytes=build_bytes + neigh_bytes, mpts_per_s=round(P / (t_b + t_n) / 1e3, 1), allocs=allocs_b + allocs_n)
-  b200._lib.status_check(dev)
+  B._lib.status_check(dev)
 
 
 def main():
@@ -597,7 +610,7 @@ def main():
                        'are for profiler captures)')
   ap.add_argument('--build-clouds', type=int, default=64,
                   help="point clouds of 200k points in the suite's octree-construction lines")
-  ap.add_argument('--mode', default='full', choices=['full', 'conv', 'suite'],
+  ap.add_argument('--mode', default='full', choices=['full', 'conv', 'suite', 'build'],
                   help="'conv' runs only the timed conv steps (no build timing, e2e or CPU baseline)")
   args = ap.parse_args()
   BATCH = args.batch
