@@ -200,6 +200,15 @@ def test_tile_table_layout_and_equivalence(mid_octree):
       y_tiled = b200.nn.conv_gather(x, w, False, bias, table, taps, cin, cout, tiles=tiles)
       y_nat = b200.nn.conv_gather(x, w, False, bias, table, taps, cin, cout, tiles=plain_tiles)
       assert torch.equal(y_plain, y_tiled) and torch.equal(y_plain, y_nat)
+      # weight gradient through the ordered table (grad_out rows are read through the row
+      # order): the same sum in another order
+      gy = torch.randn(n_out, cout, device=dev(), generator=g).to(dtype)
+      gw_plain, gb_plain = b200.nn.conv_wgrad(x, gy, table, taps, cin, cout, True)
+      gw_tiled, gb_tiled = b200.nn.conv_wgrad(x, gy, table, taps, cin, cout, True, tiles=tiles)
+      gw_nat, _ = b200.nn.conv_wgrad(x, gy, table, taps, cin, cout, False, tiles=plain_tiles)
+      assert torch.equal(gw_plain, gw_nat)
+      assert_close(to_np(gw_tiled), to_np(gw_plain), 1e-4, 'gw through the row order')
+      assert_close(to_np(gb_tiled), to_np(gb_plain), 1e-5, 'gb')
   b200._lib.status_check(dev())
   # an index past the feature rows is dropped while the tile table is built, and reported
   table, taps = octree.conv_table(6, '333', 1, False)
