@@ -236,7 +236,9 @@ int oc_tap_masks(const void* table, int idx_bytes, int table_cols, const int* h_
                  int64_t n_rows, int32_t* masks, void* stream);
 /* perm (device int32 (n_rows)) = the rows of the table sorted, stably, by oc_tap_masks: the
  * row_perm of oc_tile_table_build below.  An 8-bit LSD radix sort over the K mask bits, the same
- * kernels that sort the point keys in oc_build_octree_count.  chunk_log2 > 0: the rows are sorted
+ * kernels that sort the point keys in oc_build_octree_count.  The sort key is the mask with its
+ * bits reordered: the taps whose frequency over the table is farthest from one half are the most
+ * significant (ties: the lower tap first), so rows with a rare tap sit together.  chunk_log2 > 0: the rows are sorted
  * within consecutive chunks of 2^chunk_log2 rows only (key = chunk number, then mask), which keeps
  * the rows of a tile within one neighbourhood of the octree; 0: one sort over all rows. */
 size_t oc_tap_order_workspace_bytes(int64_t n_rows);

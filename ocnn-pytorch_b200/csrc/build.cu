@@ -509,7 +509,7 @@ extern "C" int oc_tap_masks(const void* table, int idx_bytes, int table_cols, co
 
 namespace oc {
 struct OrderLayout {
-  size_t key_a, key_b, val_a, val_b, masks, hist, scan_tmp, total;
+  size_t key_a, key_b, val_a, val_b, masks, hist, scan_tmp, counts, bitpos, total;
   int64_t sort_blocks;
 };
 static OrderLayout order_layout(int64_t n) {
@@ -525,14 +525,57 @@ static OrderLayout order_layout(int64_t n) {
   L.masks = take((size_t)m * 4);
   L.hist = take((size_t)RADIX * L.sort_blocks * 4);
   L.scan_tmp = take(scan_workspace_bytes((int64_t)RADIX * L.sort_blocks));
+  L.counts = take(32 * sizeof(unsigned long long));
+  L.bitpos = take(32 * sizeof(int));
   L.total = off;
   return L;
 }
+// counts[k] = rows whose mask has bit k: lane k of every warp keeps the count of bit k
+__global__ void tap_count_kernel(const int32_t* __restrict__ masks, int64_t n, unsigned long long* __restrict__ counts) {
+  const int lane = threadIdx.x & 31;
+  unsigned long long mine = 0;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t n_round = (n + 31) / 32 * 32;                       // whole warps take part in the ballots
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_round; i += stride) {
+    const uint32_t m = i < n ? (uint32_t)masks[i] : 0u;
+#pragma unroll
+    for (int k = 0; k < OC_MAX_TAPS; ++k) {
+      const unsigned b = __ballot_sync(0xffffffffu, (m >> k) & 1u);
+      if (lane == k) mine += __popc(b);
+    }
+  }
+  if (lane < OC_MAX_TAPS && mine) atomicAdd(&counts[lane], mine);
+}
+
+// Bit position of every tap in the sort key: the taps whose frequency is farthest from one half
+// take the most significant bits (ties: the lower tap is more significant).  Rows that hold a
+// rare tap then sit together and the other tiles skip it; the taps that about half of the rows
+// have vary inside a tile, where they waste least.
+__global__ void tap_bitpos_kernel(const unsigned long long* __restrict__ counts, int64_t n, int K, int* __restrict__ bitpos) {
+  const int t = threadIdx.x;
+  if (t >= K) return;
+  auto score = [&](int k) { const long long d = 2 * (long long)counts[k] - (long long)n; return d < 0 ? -d : d; };
+  const long long mine = score(t);
+  int rank = 0;                                      // taps that are more significant than t
+  for (int k = 0; k < K; ++k) {
+    const long long o = score(k);
+    rank += (o > mine || (o == mine && k < t)) ? 1 : 0;
+  }
+  bitpos[t] = K - 1 - rank;
+}
+
 __global__ void mask_key_kernel(const int32_t* __restrict__ masks, int64_t n, int K, int chunk_shift,
-                                uint64_t* __restrict__ key, uint32_t* __restrict__ val) {
+                                const int* __restrict__ bitpos, uint64_t* __restrict__ key,
+                                uint32_t* __restrict__ val) {
+  __shared__ int spos[OC_MAX_TAPS];
+  if (threadIdx.x < OC_MAX_TAPS) spos[threadIdx.x] = threadIdx.x < K ? bitpos[threadIdx.x] : 0;
+  __syncthreads();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    // grid1d caps the grid: a grid-stride loop.  Key = (chunk of the row, mask).
-    key[i] = ((uint64_t)(i >> chunk_shift) << K) | (uint64_t)(uint32_t)masks[i];
+    // grid1d caps the grid: a grid-stride loop.  Key = (chunk of the row, mask with its bits reordered).
+    const uint32_t m = (uint32_t)masks[i];
+    uint32_t pm = 0;
+    for (int k = 0; k < K; ++k) pm |= ((m >> k) & 1u) << spos[k];
+    key[i] = ((uint64_t)(i >> chunk_shift) << K) | (uint64_t)pm;
     val[i] = (uint32_t)i;
   }
 }
@@ -562,7 +605,12 @@ extern "C" int oc_tap_order(const void* table, int idx_bytes, int table_cols, co
   const int chunk_shift = chunk_log2 > 0 ? chunk_log2 : 31;         // 0: one chunk (n_rows < 2^31)
   int key_bits = K;
   while (((n_rows - 1) >> chunk_shift) >> (key_bits - K)) ++key_bits;   // + bits of the last chunk's number
-  mask_key_kernel<<<grid1d(n_rows), 256, 0, s>>>(masks, n_rows, K, chunk_shift, kin, vin);
+  unsigned long long* counts = (unsigned long long*)(ws + L.counts);
+  int* bitpos = (int*)(ws + L.bitpos);
+  OC_CUDA_OK(cudaMemsetAsync(counts, 0, 32 * sizeof(unsigned long long), s));
+  tap_count_kernel<<<grid1d(n_rows), 256, 0, s>>>(masks, n_rows, counts);
+  tap_bitpos_kernel<<<1, 32, 0, s>>>(counts, n_rows, K, bitpos);
+  mask_key_kernel<<<grid1d(n_rows), 256, 0, s>>>(masks, n_rows, K, chunk_shift, bitpos, kin, vin);
   OC_LAUNCH_OK("mask_key_kernel");
   const int64_t nb = L.sort_blocks;
   for (int shift = 0; shift < key_bits; shift += RADIX_BITS) {

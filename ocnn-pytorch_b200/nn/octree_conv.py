@@ -42,7 +42,10 @@ ORDER_CHUNK_LOG2 = 19   # rows are ordered by tap mask within chunks of 2^19 con
 def tap_mask_order(table, taps, chunk_log2=ORDER_CHUNK_LOG2):
   r''' Rows of `table` sorted (stably) by the bit mask of their valid taps, as an int32
   permutation.  Tiles of a tile table built in this order hold rows with the same few taps,
-  and the kernels skip the taps that are empty in a whole tile.  The sort runs within chunks
+  and the kernels skip the taps that are empty in a whole tile.  The key is the mask with its
+  bits reordered - taps whose frequency over the table is farthest from one half are the most
+  significant - so that the rows with a rare tap sit together (12.3 -> 11.2 taps per tile on
+  the benchmark's nempty table, 17.2 -> 17.0 on the full one).  The sort runs within chunks
   of ``2**chunk_log2`` consecutive rows (0: over all rows at once): rows are in z-order, so
   a chunk is a neighbourhood of the octree and the rows a tile gathers stay close in memory
   however many octrees the batch holds; half a million rows per chunk lose 3 % of the skipped

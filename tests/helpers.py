@@ -48,3 +48,20 @@ def octree_from_golden(syn):
   children = split_by(syn['child'], nnum)
   neighs = [None] + split_by(syn['neigh'].astype(np.int64), nnum[1:])
   return keys, children, neighs
+
+
+def tap_sort_key(valid, chunk_log2=0):
+  """Sort key of oc_tap_order for a (rows, K) boolean matrix of valid taps: the mask with its bits
+  reordered (taps whose frequency is farthest from one half are most significant, ties to the
+  lower tap), under the number of the row's chunk of 2**chunk_log2 rows."""
+  valid = np.asarray(valid).astype(np.int64)
+  n, K = valid.shape
+  score = np.abs(2 * valid.sum(axis=0) - n)
+  ranked = sorted(range(K), key=lambda t: (-int(score[t]), t))       # most significant first
+  bitpos = np.empty(K, np.int64)
+  for rank, t in enumerate(ranked):
+    bitpos[t] = K - 1 - rank
+  key = (valid << bitpos[None, :]).sum(axis=1)
+  if chunk_log2:
+    key = key | ((np.arange(n, dtype=np.int64) >> chunk_log2) << K)
+  return key

@@ -10,7 +10,7 @@ import torch
 
 import ocnn_pytorch_b200 as b200
 from oracle import octree_oracle as orc
-from helpers import assert_close, conv_case, octree_from_golden
+from helpers import assert_close, conv_case, octree_from_golden, tap_sort_key
 from gpu_utils import dev, to_np, build, synthetic_octree
 
 pytestmark = pytest.mark.gpu
@@ -167,9 +167,9 @@ def test_tile_table_layout_and_equivalence(mid_octree):
     raw_t = tiles.tiles
     order = to_np(tiles.perm).astype(np.int64)
     assert np.array_equal(np.sort(order), np.arange(n_out))
-    row_mask = ((to_np(table)[:, taps] >= 0) * (1 << np.arange(K))[None, :]).sum(axis=1)
-    assert (np.diff(row_mask[order]) >= 0).all()                 # mask never decreases along the table
-    assert np.array_equal(order, np.argsort(row_mask, kind='stable'))   # ties keep the table's order
+    row_key = tap_sort_key(to_np(table)[:, taps] >= 0)           # the mask, rare / ubiquitous taps in the high bits
+    assert (np.diff(row_key[order]) >= 0).all()                  # never decreases along the table
+    assert np.array_equal(order, np.argsort(row_key, kind='stable'))    # ties keep the table's order
     if transposed and stride == 2:
       cidx = to_np(octree.key(d, nempty) & 7)[order]              # which groups the rows by child index
       assert len(np.unique(cidx[:-1] != cidx[1:], return_counts=True)[1]) <= 2 and (cidx[:-1] != cidx[1:]).sum() < 64
@@ -472,7 +472,7 @@ def test_conv_error_paths(syn_octree):
 
 def test_tap_order_large_and_bad_row_order():
   # More rows than one wave of the helper kernels covers (grids are capped, kernels stride):
-  # the order is the stable sort of the rows by their mask of valid taps.
+  # the order is the stable sort of the rows by their mask of valid taps (bits reordered by frequency).
   g = torch.Generator(device=dev()).manual_seed(5)
   n, K = 148 * 16 * 256 + 12345, 27
   table = torch.randint(0, 1000, (n, K), device=dev(), generator=g)
@@ -480,17 +480,15 @@ def test_tap_order_large_and_bad_row_order():
   table[: n // 3, 9:] = -1                        # many rows share few masks
   taps = list(range(K))
   order = to_np(b200.nn.tap_mask_order(table, taps, 0)).astype(np.int64)
-  masks = ((to_np(table) >= 0) * (1 << np.arange(K))[None, :]).sum(axis=1)
-  assert np.array_equal(order, np.argsort(masks, kind='stable'))
+  valid = to_np(table) >= 0
+  assert np.array_equal(order, np.argsort(tap_sort_key(valid), kind='stable'))
   # within chunks of 2^17 rows (the default is 2^19: two chunks here)
   for lg in (17, 19):
     order_c = to_np(b200.nn.tap_mask_order(table, taps, lg)).astype(np.int64)
-    key = ((np.arange(n) >> lg) << K) | masks
-    assert np.array_equal(order_c, np.argsort(key, kind='stable'))
+    assert np.array_equal(order_c, np.argsort(tap_sort_key(valid, lg), kind='stable'))
   # fewer taps than a sort pass, and a single row
   order5 = to_np(b200.nn.tap_mask_order(table[:5000], [3, 0, 7], 10)).astype(np.int64)
-  m5 = ((to_np(table[:5000])[:, [3, 0, 7]] >= 0) * np.array([1, 2, 4])[None, :]).sum(axis=1)
-  assert np.array_equal(order5, np.argsort(((np.arange(5000) >> 10) << 3) | m5, kind='stable'))
+  assert np.array_equal(order5, np.argsort(tap_sort_key(valid[:5000][:, [3, 0, 7]], 10), kind='stable'))
   assert to_np(b200.nn.tap_mask_order(table[:1], taps)).tolist() == [0]
   # a row order that is not a permutation of the rows is reported when the tile table is built
   small = table[:1000].contiguous()
