@@ -121,16 +121,27 @@ radix_hist_kernel(const uint64_t* __restrict__ key, int64_t n, int shift,
   }
 }
 
+// Scatter pass.  The block first orders its own tile by digit in shared memory (stable: warp,
+// round, lane), then copies it out position by position: position j of the ordered tile, digit
+// d, goes to (start of the block's run of digit d in the output) + (j - start of digit d in the
+// tile), so consecutive threads write consecutive addresses within a run instead of 256 scattered
+// buckets per warp.
 __global__ void __launch_bounds__(SORT_THREADS)
 radix_scatter_kernel(const uint64_t* __restrict__ key_in, const uint32_t* __restrict__ val_in,
                      int64_t n, int shift, const uint32_t* __restrict__ hist_scanned,
                      int64_t nblocks, uint64_t* __restrict__ key_out,
                      uint32_t* __restrict__ val_out) {
   __shared__ int wh[SORT_WARPS][RADIX];
+  __shared__ int64_t gdelta[RADIX];            // output position of tile position j with digit d = gdelta[d] + j
+  __shared__ int wsum[SORT_WARPS];
+  __shared__ uint64_t skey[SORT_TILE];
+  __shared__ uint32_t sval[SORT_TILE];
+  static_assert(RADIX == SORT_THREADS, "one thread per digit in the offset step");
   for (int i = threadIdx.x; i < SORT_WARPS * RADIX; i += SORT_THREADS) (&wh[0][0])[i] = 0;
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t base = (int64_t)blockIdx.x * SORT_TILE + (int64_t)warp * (32 * SORT_ITEMS);
+  const int64_t tile0 = (int64_t)blockIdx.x * SORT_TILE;
+  const int64_t base = tile0 + (int64_t)warp * (32 * SORT_ITEMS);
   uint64_t k[SORT_ITEMS];
 #pragma unroll
   for (int r = 0; r < SORT_ITEMS; ++r) {
@@ -140,9 +151,26 @@ radix_scatter_kernel(const uint64_t* __restrict__ key_in, const uint32_t* __rest
     warp_digit_count(wh[warp], (int)((k[r] >> shift) & (RADIX - 1)), valid);
   }
   __syncthreads();
-  // per digit: global start of this block, then exclusive offsets per warp
-  for (int d = threadIdx.x; d < RADIX; d += SORT_THREADS) {
-    int run = (int)hist_scanned[(int64_t)d * nblocks + blockIdx.x];
+  {
+    // thread d: the tile's count of digit d, its exclusive prefix over the digits (start of digit d in
+    // the ordered tile), then the start of every warp's share
+    const int d = threadIdx.x;
+    int total = 0;
+#pragma unroll
+    for (int w = 0; w < SORT_WARPS; ++w) total += wh[w][d];
+    int incl = total;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    int before = 0;
+#pragma unroll
+    for (int w = 0; w < SORT_WARPS; ++w) before += w < warp ? wsum[w] : 0;
+    int run = before + incl - total;             // start of digit d in the ordered tile
+    gdelta[d] = (int64_t)hist_scanned[(int64_t)d * nblocks + blockIdx.x] - run;
 #pragma unroll
     for (int w = 0; w < SORT_WARPS; ++w) {
       const int c = wh[w][d];
@@ -159,12 +187,21 @@ radix_scatter_kernel(const uint64_t* __restrict__ key_in, const uint32_t* __rest
     const unsigned peers = __match_any_sync(0xffffffffu, valid ? d : RADIX);
     if (valid) {
       const int pos = wh[warp][d] + __popc(peers & ((1u << lane) - 1u));
-      key_out[pos] = k[r];
-      val_out[pos] = val_in[i];
+      skey[pos] = k[r];
+      sval[pos] = val_in[i];
     }
     __syncwarp();
     if (valid && (__ffs(peers) - 1) == lane) wh[warp][d] += __popc(peers);
     __syncwarp();
+  }
+  __syncthreads();
+  const int64_t left = n - tile0;
+  const int cnt = (int)(left < SORT_TILE ? left : SORT_TILE);
+  for (int j = threadIdx.x; j < cnt; j += SORT_THREADS) {
+    const uint64_t kk = skey[j];
+    const int64_t pos = gdelta[(int)((kk >> shift) & (RADIX - 1))] + j;
+    key_out[pos] = kk;
+    val_out[pos] = sval[j];
   }
 }
 
