@@ -426,9 +426,14 @@ def run_conv_only(args, b200, octree, dev):
 LAST_DEVICE_ALLOCS = 0   # cudaMalloc calls of torch's allocator inside the last timed region of _time
 
 
+SUITE_REPS, SUITE_WARM = None, None   # --suite-reps / --suite-warm: overrides for profiler captures
+
+
 def _time(fn, reps=10, warm=3):
   import torch
   global LAST_DEVICE_ALLOCS
+  reps = SUITE_REPS or reps
+  warm = SUITE_WARM if SUITE_WARM is not None else warm
   for _ in range(warm):
     fn()
   torch.cuda.synchronize()
@@ -610,9 +615,14 @@ def main():
                        'are for profiler captures)')
   ap.add_argument('--build-clouds', type=int, default=64,
                   help="point clouds of 200k points in the suite's octree-construction lines")
+  ap.add_argument('--suite-reps', type=int, default=None,
+                  help='timed launches per suite line (default 10; 1 for a short profiler capture)')
+  ap.add_argument('--suite-warm', type=int, default=None, help='warm-up launches per suite line (default 3)')
   ap.add_argument('--mode', default='full', choices=['full', 'conv', 'suite', 'build'],
                   help="'conv' runs only the timed conv steps (no build timing, e2e or CPU baseline)")
   args = ap.parse_args()
+  global SUITE_REPS, SUITE_WARM
+  SUITE_REPS, SUITE_WARM = args.suite_reps, args.suite_warm
   BATCH = args.batch
   if args.impl == 'reference':
     run_reference(args)
