@@ -224,13 +224,13 @@ __global__ void dwconv_wgrad_kernel(const T* __restrict__ data, const T* __restr
 // (row lane rl, 16-byte channel vector v) walks the rows rl, rl + RL, ... of the split, loads
 // grad_out once per row and the gathered row once per tap (16 bytes each), and keeps the
 // DWG_TAPS x N partial sums of its channels in registers; row lanes are folded through
-// shared memory tap by tap.  Small tap groups win: with 3 taps per block the index loads and the
-// row loads of a row are issued together and the kernel keeps enough warps resident; 9 taps per
-// block need 72 accumulators per thread and run 1.5x - 3x slower although grad_out is then read
-// 3 instead of 9 times.  (The scalar kernel above issues one 2-byte load per channel, tap and
-// row: 35 ms against 9.6 ms on the 4 M-row, C = 256 case.)
+// shared memory tap by tap.  The blocks of one row split (one per tap group) run together and
+// share the split's rows through L2.  Measured on the 4 M-row, C = 256 case with 1 / 2 / 3 / 5 / 9
+// taps per block: 11.2 / 6.6 / 7.5 / 10.5 / 16.9 ms - few taps keep the accumulators small and many
+// warps resident, one tap reads grad_out 27 times.  (The scalar kernel above issues one 2-byte
+// load per channel, tap and row: 35 ms.)
 #ifndef OC_DWG_TAPS
-#define OC_DWG_TAPS 3
+#define OC_DWG_TAPS 2
 #endif
 constexpr int DWG_TAPS = OC_DWG_TAPS;
 constexpr int DWG_THREADS = 256;
