@@ -281,16 +281,24 @@ __global__ void __launch_bounds__(THREADS, 1) wgrad_tc_kernel(const Params p) {
     cp_async_wait_all();
   } else if (warp == LOADER_WARP) {
     // ===================================================================== index loader
-    // Per row tile: the tile-table block, one bulk copy issued by lane 0.
+    // Per row tile: the header of the tile-table block and the index rows of the taps this CTA's
+    // M tiles cover (a contiguous range of taps), two bulk copies issued by lane 0.
     const uint8_t* src = (const uint8_t*)p.tiled;
+    const int b_lo = 2 * m_lo, b_hi = min(p.nblk, 2 * (m_lo + m_cnt));      // blocks of this CTA
+    const int k_first = p.PACK > 1 ? b_lo * p.PACK : b_lo / p.KB;
+    const int k_end = min(p.K, p.PACK > 1 ? b_hi * p.PACK : (b_hi + p.KB - 1) / p.KB);
+    const uint32_t rows_off = IDX_HDR_BYTES + (uint32_t)k_first * TILE_R * 4;
+    const uint32_t rows_len = (uint32_t)(k_end - k_first) * TILE_R * 4;
     uint32_t it = 0;
     for (int64_t tile = t_begin; tile < t_end; tile += t_step, ++it) {
       const int b = (int)(it & 1u);
       if (it >= 2 && !mbar_wait(iempty_bar(b), ((it >> 1) - 1u) & 1u, abort_flag, &g_tc_status, 10)) break;
       if (lane == 0) {
-        mbar_arrive_expect_tx(ifull_bar(b), p.tiled_block_bytes);
-        bulk_g2s(s_base + L.sidx + b * IDX_BUF_BYTES, src + (size_t)tile * p.tiled_block_bytes, p.tiled_block_bytes,
-                 ifull_bar(b));
+        const uint8_t* blk = src + (size_t)tile * p.tiled_block_bytes;
+        const uint32_t dst = s_base + L.sidx + b * IDX_BUF_BYTES;
+        mbar_arrive_expect_tx(ifull_bar(b), IDX_HDR_BYTES + rows_len);
+        bulk_g2s(dst, blk, IDX_HDR_BYTES, ifull_bar(b));
+        bulk_g2s(dst + rows_off, blk + rows_off, rows_len, ifull_bar(b));
       }
       __syncwarp();
     }
