@@ -16,7 +16,8 @@
 // group with at least one valid neighbour, gathers the two blocks and issues
 // 8 MMAs (K = 16 rows each) into that M tile's own TMEM accumulator, which stays
 // resident for the whole slice.
-// Roles: a loader warp brings in, per row tile, the tile-table block (one bulk copy); four
+// Roles: a loader warp brings in, per row tile, the tile-table block's header and the index rows
+// of this CTA's taps (two bulk copies); four
 // warps load the grad_out tile, a quarter each (with one warp this load bounds the kernel when
 // Cout >= 128); eight producer warps gather, each owning whole 64-channel blocks
 // dealt round-robin (so a warp keeps a block of its own in flight while the others work
