@@ -36,22 +36,25 @@ class TileTable:
     self.perm = perm
 
 
-ORDER_CHUNK_LOG2 = 19   # rows are ordered by tap mask within chunks of 2^19 consecutive rows
+ORDER_CHUNK_LOG2 = 19   # tables of more than 2^21 rows are ordered by tap mask within chunks of 2^19 consecutive rows
 
 
-def tap_mask_order(table, taps, chunk_log2=ORDER_CHUNK_LOG2):
+def tap_mask_order(table, taps, chunk_log2=None):
   r''' Rows of `table` sorted (stably) by the bit mask of their valid taps, as an int32
   permutation.  Tiles of a tile table built in this order hold rows with the same few taps,
   and the kernels skip the taps that are empty in a whole tile.  The key is the mask with its
   bits reordered - taps whose frequency over the table is farthest from one half are the most
   significant - so that the rows with a rare tap sit together (12.3 -> 11.2 taps per tile on
   the benchmark's nempty table, 17.2 -> 17.0 on the full one).  The sort runs within chunks
-  of ``2**chunk_log2`` consecutive rows (0: over all rows at once): rows are in z-order, so
+  of ``2**chunk_log2`` consecutive rows (0: over all rows at once; default: 2**19 for tables of
+  more than 2**21 rows, else all rows at once): rows are in z-order, so
   a chunk is a neighbourhood of the octree and the rows a tile gathers stay close in memory
   however many octrees the batch holds; half a million rows per chunk lose 3 % of the skipped
   taps of the global order and run 2 % faster on the 4 M-row benchmark level. '''
   _lib.require_cuda(table)
   n = table.shape[0]
+  if chunk_log2 is None:      # tables of up to 2^21 rows are sorted as a whole (3 % faster at 1 M rows)
+    chunk_log2 = ORDER_CHUNK_LOG2 if n > (1 << 21) else 0
   perm = torch.empty(n, dtype=torch.int32, device=table.device)
   ws = _lib.workspace(_lib.lib().oc_tap_order_workspace_bytes(n), table.device)
   _lib.call('oc_tap_order', _lib.ptr(table), _idx_bytes(table), table.shape[1], _lib.int_array(taps), len(taps), n,
